@@ -1,0 +1,152 @@
+// minGRU: a gated recurrence whose gates read only the current token, so that a prompt is a linear scan.
+//
+//   z = sigmoid(a_z),  c = a_x + 1/2 where a_x >= 0, sigmoid(a_x) below,
+//   S_t = (1 - z) S_(t-1) + z c      (element by element, fp32, state carried per request)
+//   y_t = S_t * silu(a_g)
+//
+// a = [a_z | a_x | a_g] is the fp32 output of one projection, [n, 3W].  Everything here is fp32; y is written in
+// the activation dtype for the output projection.
+//
+// Two routes.  Few tokens per request: one thread per (request, channel) walks the request's tokens.  Long portions:
+// the tokens are cut into chunks; every chunk is scanned from a zero state and gives the pair (A, B) with
+// S_end = A S_start + B; a second pass walks the chunks of a request in order and leaves every chunk's starting
+// state; a third pass scans every chunk again from its starting state and writes y.  The state a request starts
+// from is its slot's, or zero at position 0 whatever the slot still holds.
+#include "common.cuh"
+
+__device__ __forceinline__ float sigmoid_f32(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+__device__ __forceinline__ void mingru_gate(float az, float ax, float& keep, float& add) {
+    const float z = sigmoid_f32(az);
+    const float c = ax >= 0.0f ? ax + 0.5f : sigmoid_f32(ax);
+    keep = 1.0f - z;
+    add = z * c;
+}
+
+// req_meta [requests, 4] = (first token, tokens, ., .) or null: every request is one token, request r is token r
+template <typename T>
+__global__ void mingru_walk_kernel(const float* __restrict__ a, T* __restrict__ y, float* __restrict__ state,
+                                   const int32_t* __restrict__ req_meta, const int32_t* __restrict__ slots,
+                                   const int32_t* __restrict__ positions, int W) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int r = blockIdx.y;
+    if (c >= W) return;
+    const int t0 = req_meta ? req_meta[4 * r] : r;
+    const int n = req_meta ? req_meta[4 * r + 1] : 1;
+    float* st = state + (size_t)slots[r] * W + c;
+    float S = positions[t0] == 0 ? 0.0f : *st;
+    for (int t = t0; t < t0 + n; ++t) {
+        const float* row = a + (size_t)t * 3 * W;
+        float keep, add;
+        mingru_gate(row[c], row[W + c], keep, add);
+        S = fmaf(keep, S, add);
+        const float g = row[2 * W + c];
+        y[(size_t)t * W + c] = from_f32<T>(S * (g * sigmoid_f32(g)));
+    }
+    *st = S;
+}
+
+// pass 1: chunk k of request r (tokens t0 + k*chunk ...) from a zero state -> A[ck], B[ck]
+__global__ void mingru_chunk_reduce_kernel(const float* __restrict__ a, float* __restrict__ A, float* __restrict__ B,
+                                           const int32_t* __restrict__ chunk_meta, int W) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int ck = blockIdx.y;
+    if (c >= W) return;
+    const int t0 = chunk_meta[4 * ck], n = chunk_meta[4 * ck + 1];
+    float prod = 1.0f, S = 0.0f;
+    for (int t = t0; t < t0 + n; ++t) {
+        const float* row = a + (size_t)t * 3 * W;
+        float keep, add;
+        mingru_gate(row[c], row[W + c], keep, add);
+        S = fmaf(keep, S, add);
+        prod *= keep;
+    }
+    A[(size_t)ck * W + c] = prod;
+    B[(size_t)ck * W + c] = S;
+}
+
+// pass 2: per request, in chunk order: B[ck] <- the state the chunk starts from; the slot gets the final state.
+// chunk_meta [chunks, 4] = (first token, tokens, request, first chunk of the request ? 1 : 0); req_chunks [requests, 2]
+// = (first chunk, chunks).
+__global__ void mingru_chunk_carry_kernel(const float* __restrict__ A, float* __restrict__ B, float* __restrict__ state,
+                                          const int32_t* __restrict__ req_chunks, const int32_t* __restrict__ chunk_meta,
+                                          const int32_t* __restrict__ slots, const int32_t* __restrict__ positions, int W) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int r = blockIdx.y;
+    if (c >= W) return;
+    const int k0 = req_chunks[2 * r], nk = req_chunks[2 * r + 1];
+    if (nk == 0) return;
+    float* st = state + (size_t)slots[r] * W + c;
+    float S = positions[chunk_meta[4 * k0]] == 0 ? 0.0f : *st;
+    for (int k = k0; k < k0 + nk; ++k) {
+        const size_t i = (size_t)k * W + c;
+        const float start = S;
+        S = fmaf(A[i], S, B[i]);
+        B[i] = start;
+    }
+    *st = S;
+}
+
+// pass 3: every chunk again from its starting state, writing y
+template <typename T>
+__global__ void mingru_chunk_apply_kernel(const float* __restrict__ a, const float* __restrict__ start, T* __restrict__ y,
+                                          const int32_t* __restrict__ chunk_meta, int W) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int ck = blockIdx.y;
+    if (c >= W) return;
+    const int t0 = chunk_meta[4 * ck], n = chunk_meta[4 * ck + 1];
+    float S = start[(size_t)ck * W + c];
+    for (int t = t0; t < t0 + n; ++t) {
+        const float* row = a + (size_t)t * 3 * W;
+        float keep, add;
+        mingru_gate(row[c], row[W + c], keep, add);
+        S = fmaf(keep, S, add);
+        const float g = row[2 * W + c];
+        y[(size_t)t * W + c] = from_f32<T>(S * (g * sigmoid_f32(g)));
+    }
+}
+
+MM_EXPORT int mm_mingru_walk(const void* a, void* y, int dtype, void* state, const void* req_meta, const void* slots,
+                             const void* positions, int n_requests, int W, void* stream) {
+    MM_REQUIRE(n_requests >= 0 && W > 0, "mingru: bad sizes");
+    if (n_requests == 0) return MM_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = W >= 128 ? 128 : 64;
+    dim3 grid(ceil_div(W, threads), n_requests);
+    if (dtype == MM_F32)
+        mm_launch(mingru_walk_kernel<float>, grid, dim3(threads), 0, s, (const float*)a, (float*)y, (float*)state,
+                  (const int32_t*)req_meta, (const int32_t*)slots, (const int32_t*)positions, W);
+    else if (dtype == MM_BF16)
+        mm_launch(mingru_walk_kernel<__nv_bfloat16>, grid, dim3(threads), 0, s, (const float*)a, (__nv_bfloat16*)y, (float*)state,
+                  (const int32_t*)req_meta, (const int32_t*)slots, (const int32_t*)positions, W);
+    else
+        MM_REQUIRE(false, "mingru: dtype must be float32 or bfloat16");
+    MM_CHECK_LAUNCH();
+    return MM_OK;
+}
+
+MM_EXPORT int mm_mingru_chunked(const void* a, void* y, int dtype, void* state, void* A, void* B, const void* chunk_meta,
+                                const void* req_chunks, const void* slots, const void* positions, int n_requests, int n_chunks,
+                                int W, void* stream) {
+    MM_REQUIRE(n_requests >= 0 && n_chunks >= 0 && W > 0, "mingru: bad sizes");
+    if (n_requests == 0 || n_chunks == 0) return MM_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = W >= 128 ? 128 : 64;
+    const int bx = ceil_div(W, threads);
+    mm_launch(mingru_chunk_reduce_kernel, dim3(bx, n_chunks), dim3(threads), 0, s, (const float*)a, (float*)A, (float*)B,
+              (const int32_t*)chunk_meta, W);
+    MM_CHECK_LAUNCH();
+    mm_launch(mingru_chunk_carry_kernel, dim3(bx, n_requests), dim3(threads), 0, s, (const float*)A, (float*)B, (float*)state,
+              (const int32_t*)req_chunks, (const int32_t*)chunk_meta, (const int32_t*)slots, (const int32_t*)positions, W);
+    MM_CHECK_LAUNCH();
+    if (dtype == MM_F32)
+        mm_launch(mingru_chunk_apply_kernel<float>, dim3(bx, n_chunks), dim3(threads), 0, s, (const float*)a, (const float*)B,
+                  (float*)y, (const int32_t*)chunk_meta, W);
+    else if (dtype == MM_BF16)
+        mm_launch(mingru_chunk_apply_kernel<__nv_bfloat16>, dim3(bx, n_chunks), dim3(threads), 0, s, (const float*)a,
+                  (const float*)B, (__nv_bfloat16*)y, (const int32_t*)chunk_meta, W);
+    else
+        MM_REQUIRE(false, "mingru: dtype must be float32 or bfloat16");
+    MM_CHECK_LAUNCH();
+    return MM_OK;
+}

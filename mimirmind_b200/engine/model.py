@@ -81,9 +81,14 @@ class Model:
             groups.append(GroupSpec(name + (f"_w{w}" if w else "_full"), tuple(entries), g, hd, w, arrays))
         return groups
 
+    EMBEDDING_STATE = -1      # the key of the embedding's state among the schedule entries' (which count from 0)
+
     def state_specs(self) -> Dict[int, StateSpec]:
-        """Schedule entries that own fixed-size per-request state."""
+        """Schedule entries that own fixed-size per-request state, and the embedding (key EMBEDDING_STATE) if it does."""
         out = {}
+        emb = getattr(self.embedding, "state_spec", None)
+        if emb is not None and emb() is not None:
+            out[self.EMBEDDING_STATE] = emb()
         for i, e in enumerate(self.schedule):
             if e.cache_from is not None:
                 continue

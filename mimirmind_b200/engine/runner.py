@@ -214,7 +214,10 @@ class ModelRunner:
         if self.native is not None and dump is None and not ctx.plain_only:
             return self.native.forward(ctx)
         m = self.model
-        residual = m.embedding.forward(ctx.token_ids)
+        if hasattr(m.embedding, "embed"):
+            residual = m.embedding.embed(ctx, self.storage.states.get(m.EMBEDDING_STATE))
+        else:
+            residual = m.embedding.forward(ctx.token_ids)
         if dump is not None:
             dump.write(0, "inp_scaled", residual)
         pending = None

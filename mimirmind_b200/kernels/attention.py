@@ -21,3 +21,12 @@ def paged_attention(q, cache, out, ctx, num_heads: int, num_kv_heads: int, head_
             return attention_bf16.run(q, cache, out, ctx, num_heads, num_kv_heads, head_dim, window, scale)
     return ops.attention_generic(q, cache.k_pages, cache.v_pages, out, ctx.positions, ctx.token_req,
                                  cache.block_table, cache.page_size, num_heads, num_kv_heads, head_dim, window, scale)
+
+
+def paged_sink_attention(q, cache, out, ctx, num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int, window: int,
+                         scale: float, sink: bool) -> torch.Tensor:
+    """Windowed attention with a softmax sink over pools of keys ``[pages, G, page, key_dim]`` and values
+    ``[pages, G, page, value_dim]``."""
+    return ops.attention_sink_generic(q, cache.arrays["k"], cache.arrays["v"], out, ctx.positions, ctx.token_req,
+                                      cache.block_table, cache.page_size, num_heads, num_kv_heads, key_dim, value_dim, window,
+                                      scale, sink)

@@ -51,6 +51,14 @@ _PROTOTYPES = {
     "mm_sample_rows": [P, P, I, I, P, P, P, P, P, P],
     "mm_apply_penalties": [P, I, I, P, I, P, P, P, P, P],
     "mm_window_push": [P, I, I, P, P, P, P],
+    "mm_group_norm_chain": [P, P, P, P, I, P, P, I, I, I, I, F, P],
+    "mm_group_norm_rows": [P, P, I, P, I, I, I, I, F, P],
+    "mm_embedding_bigram": [P, P, P, P, P, P, P, P, I, P, I, I, I, I, c_longlong, c_longlong, P],
+    "mm_qkv_pairs_post": [P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P],
+    "mm_attention_sink_generic": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
+    "mm_mingru_walk": [P, P, I, P, P, P, P, I, I, P],
+    "mm_mingru_chunked": [P, P, I, P, P, P, P, P, P, P, I, I, I, P],
+    "mm_bias_act": [P, P, I, P, I, I, I, I, P],
 }
 
 

@@ -596,3 +596,205 @@ def window_push(recent: torch.Tensor, widths: torch.Tensor, lengths: torch.Tenso
 def uniform_from(seed: int, counter: int) -> float:
     """The uniform number in [0,1) the device sampler draws for (seed, counter)."""
     return float(_lib.load().mm_uniform_from(seed & 0xFFFFFFFFFFFFFFFF, counter & 0xFFFFFFFFFFFFFFFF))
+
+
+# ---- grouped norm, bigram embedding, sink attention, minGRU, bias + activation ------------------------------------------
+def group_norm_chain(residual: torch.Tensor, branch: Optional[torch.Tensor], w_post: Optional[torch.Tensor],
+                     w_next: Optional[torch.Tensor], groups: int, eps: float, out: Optional[torch.Tensor] = None,
+                     rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """RMS norm in ``groups`` equal parts of a row, chained around the residual stream (fp32, in place):
+    ``residual += gnorm(branch) * w_post`` (plain add without ``w_post``), then ``out = gnorm(residual) * w_next``.
+    Either half may be absent.  With ``rows`` output row i comes from source row rows[i] and nothing is added."""
+    _need(residual, "group norm residual", torch.float32)
+    d = residual.shape[-1]
+    weight = w_post if w_post is not None else w_next
+    if weight is None and branch is None:
+        raise KernelError("group norm: nothing to do")
+    for w in (w_post, w_next):
+        if w is not None:
+            _need(w, "group norm weight")
+            if w.shape != (d,) or w.dtype != weight.dtype:
+                raise KernelError("group norm: weight shape or dtype mismatch")
+    if branch is not None:
+        _need(branch, "group norm branch")
+        if branch.shape != residual.shape:
+            raise KernelError("group norm: branch and residual differ in shape")
+    if w_next is not None:
+        _need(out, "group norm out")
+        if out.shape[-1] != d or (branch is not None and out.dtype != branch.dtype):
+            raise KernelError("group norm: out width or dtype mismatch")
+    if rows is not None:
+        _need(rows, "group norm rows", torch.int32)
+        if out is None or rows.numel() != out.shape[0]:
+            raise KernelError("group norm: rows and out differ in length")
+    n_out = out.shape[0] if out is not None else residual.shape[0]
+    if rows is None and n_out != residual.shape[0]:
+        raise KernelError("group norm: out and residual differ in rows")
+    act = out.dtype if out is not None else branch.dtype
+    check(_lib.load().mm_group_norm_chain(residual.data_ptr(), _ptr(branch), _ptr(w_post), _ptr(w_next),
+                                          dtype_code(weight.dtype) if weight is not None else dtype_code(act), _ptr(rows), _ptr(out),
+                                          dtype_code(act), n_out, d, int(groups), float(eps), _stream()), "group_norm_chain")
+    return out
+
+
+def group_norm_rows(x: torch.Tensor, weight: torch.Tensor, groups: int, eps: float, out: torch.Tensor) -> torch.Tensor:
+    """out = gnorm(x) * weight for rows in the activation dtype."""
+    _need(x, "group norm x")
+    _need(weight, "group norm weight")
+    _need(out, "group norm out", x.dtype)
+    n, d = x.shape
+    if weight.shape != (d,) or out.shape != x.shape:
+        raise KernelError("group norm: shape mismatch")
+    check(_lib.load().mm_group_norm_rows(x.data_ptr(), weight.data_ptr(), dtype_code(weight.dtype), out.data_ptr(), dtype_code(x.dtype),
+                                         n, d, int(groups), float(eps), _stream()), "group_norm_rows")
+    return out
+
+
+def embedding_bigram(ids: torch.Tensor, positions: torch.Tensor, token_req: torch.Tensor, req_meta: Optional[torch.Tensor],
+                     slots: torch.Tensor, state: torch.Tensor, table: torch.Tensor, pairs: torch.Tensor, out: torch.Tensor,
+                     buckets: int, mul_prev: int, mul_cur: int) -> torch.Tensor:
+    """out[t] = table[id_t] + pairs[(prev_t * mul_prev + id_t * mul_cur) mod buckets] (row ``buckets`` at position 0) as fp32.
+    ``state`` [slots] int32 carries every request's last token from step to step; ``req_meta`` [requests, 4] gives each
+    request's first token and token count in this step (None: one token per request)."""
+    _need(ids, "embedding ids", torch.int32)
+    _need(positions, "positions", torch.int32)
+    _need(token_req, "token_req", torch.int32)
+    _need(slots, "state slots", torch.int32)
+    _need(state, "bigram state", torch.int32)
+    _need(table, "embedding table")
+    _need(pairs, "bigram table", table.dtype)
+    _need(out, "embedding out", torch.float32)
+    n, (v, d) = ids.numel(), table.shape
+    if pairs.shape != (buckets + 1, d) or out.shape != (n, d):
+        raise KernelError("bigram embedding: the pair table must be [buckets + 1, width] and out [tokens, width]")
+    if req_meta is not None:
+        _need(req_meta, "req_meta", torch.int32)
+    check(_lib.load().mm_embedding_bigram(ids.data_ptr(), positions.data_ptr(), token_req.data_ptr(), _ptr(req_meta), slots.data_ptr(),
+                                          state.data_ptr(), table.data_ptr(), pairs.data_ptr(), dtype_code(table.dtype), out.data_ptr(),
+                                          n, v, d, int(buckets), int(mul_prev), int(mul_cur), _stream()), "embedding_bigram")
+    return out
+
+
+def qkv_pairs_post(qkv: torch.Tensor, q_out: torch.Tensor, k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
+                   v_first: Optional[torch.Tensor], inv_freq: torch.Tensor, positions: torch.Tensor, token_req: torch.Tensor,
+                   block_table: torch.Tensor, page_size: int, num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int,
+                   rot_dims: int, mix_mode: int, mix: float) -> None:
+    """Rotates adjacent pairs of q and k by position (angle = position * inv_freq[i], fp32), mixes the values
+    (mode 1: copy them to ``v_first``; 2: v = (1 - mix) v + mix v_first), writes q to ``q_out`` and k and the mixed v
+    into their pages ([pages, kv heads, page, key_dim] and [.., value_dim])."""
+    _need(qkv, "qkv")
+    n = qkv.shape[0]
+    H, G, dk, dv = num_heads, num_kv_heads, key_dim, value_dim
+    if qkv.shape != (n, (H + G) * dk + G * dv):
+        raise KernelError(f"qkv: shape {tuple(qkv.shape)} is not [n, {(H + G) * dk + G * dv}]")
+    _need(q_out, "q_out", qkv.dtype)
+    if q_out.shape != (n, H * dk):
+        raise KernelError("q_out: wrong shape")
+    if k_pages is not None:
+        _need(k_pages, "k_pages", qkv.dtype)
+        _need(v_pages, "v_pages", qkv.dtype)
+        if k_pages.shape[1:] != (G, page_size, dk) or v_pages.shape[1:] != (G, page_size, dv) or k_pages.shape[0] != v_pages.shape[0]:
+            raise KernelError("qkv post: page pool shape mismatch")
+    if mix_mode:
+        _need(v_first, "v_first", qkv.dtype)
+        if v_first.shape != (n, G * dv):
+            raise KernelError("v_first: wrong shape")
+    _need(inv_freq, "inv_freq", torch.float32)
+    if inv_freq.numel() < rot_dims // 2:
+        raise KernelError("inv_freq: too short")
+    _need(positions, "positions", torch.int32)
+    _need(token_req, "token_req", torch.int32)
+    _need(block_table, "block_table", torch.int32)
+    check(_lib.load().mm_qkv_pairs_post(qkv.data_ptr(), q_out.data_ptr(), _ptr(k_pages), _ptr(v_pages), _ptr(v_first) if mix_mode else None,
+                                        dtype_code(qkv.dtype), inv_freq.data_ptr(), positions.data_ptr(), token_req.data_ptr(),
+                                        block_table.data_ptr(), block_table.shape[1], page_size, n, H, G, dk, dv, int(rot_dims),
+                                        int(mix_mode), float(mix), _stream()), "qkv_pairs_post")
+
+
+def attention_sink_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor, positions: torch.Tensor,
+                           token_req: torch.Tensor, block_table: torch.Tensor, page_size: int, num_heads: int, num_kv_heads: int,
+                           key_dim: int, value_dim: int, window: int, scale: float, sink: bool) -> torch.Tensor:
+    """Windowed causal attention of every token over its request's pages with keys of ``key_dim`` and values of
+    ``value_dim``; with ``sink`` the softmax denominator has one added (fp32 arithmetic, any sizes)."""
+    _need(q, "attention q")
+    n = q.shape[0]
+    _need(out, "attention out", q.dtype)
+    _need(k_pages, "attention k_pages", q.dtype)
+    _need(v_pages, "attention v_pages", q.dtype)
+    if q.shape != (n, num_heads * key_dim) or out.shape != (n, num_heads * value_dim):
+        raise KernelError("attention: q/out shape mismatch")
+    if k_pages.shape[1:] != (num_kv_heads, page_size, key_dim) or v_pages.shape[1:] != (num_kv_heads, page_size, value_dim):
+        raise KernelError("attention: page pool shape mismatch")
+    _need(positions, "positions", torch.int32)
+    _need(token_req, "token_req", torch.int32)
+    _need(block_table, "block_table", torch.int32)
+    check(_lib.load().mm_attention_sink_generic(
+        q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), dtype_code(q.dtype), positions.data_ptr(),
+        token_req.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size, n, num_heads, num_kv_heads, key_dim,
+        value_dim, int(window), float(scale), int(bool(sink)), _stream()), "attention_sink_generic")
+    return out
+
+
+def mingru_walk(a: torch.Tensor, y: torch.Tensor, state: torch.Tensor, req_meta: Optional[torch.Tensor], slots: torch.Tensor,
+                positions: torch.Tensor, n_requests: int) -> torch.Tensor:
+    """minGRU over each request's tokens in order, one thread per (request, channel): ``a`` [n, 3W] fp32 holds the
+    projections for the gate, the candidate and the output gate; ``state`` [slots, W] fp32 is read and left updated;
+    ``y`` [n, W] gets state * silu(output gate)."""
+    _need(a, "mingru projections", torch.float32)
+    _need(y, "mingru out")
+    _need(state, "mingru state", torch.float32)
+    _need(slots, "state slots", torch.int32)
+    _need(positions, "positions", torch.int32)
+    n, w3 = a.shape
+    W = w3 // 3
+    if w3 != 3 * W or y.shape != (n, W) or state.shape[-1] != W:
+        raise KernelError("mingru: shape mismatch")
+    if req_meta is not None:
+        _need(req_meta, "req_meta", torch.int32)
+    check(_lib.load().mm_mingru_walk(a.data_ptr(), y.data_ptr(), dtype_code(y.dtype), state.data_ptr(), _ptr(req_meta), slots.data_ptr(),
+                                     positions.data_ptr(), int(n_requests), W, _stream()), "mingru_walk")
+    return y
+
+
+def mingru_chunked(a: torch.Tensor, y: torch.Tensor, state: torch.Tensor, chunk_meta: torch.Tensor, req_chunks: torch.Tensor,
+                   slots: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+    """minGRU as a scan over chunks of tokens (three launches: every chunk from a zero state, the carry along each
+    request's chunks, every chunk again from its starting state).  ``chunk_meta`` [chunks, 4] = (first token, tokens,
+    request, .), ``req_chunks`` [requests, 2] = (first chunk, chunks)."""
+    _need(a, "mingru projections", torch.float32)
+    _need(y, "mingru out")
+    _need(state, "mingru state", torch.float32)
+    _need(chunk_meta, "chunk_meta", torch.int32)
+    _need(req_chunks, "req_chunks", torch.int32)
+    _need(slots, "state slots", torch.int32)
+    _need(positions, "positions", torch.int32)
+    n, w3 = a.shape
+    W = w3 // 3
+    if w3 != 3 * W or y.shape != (n, W) or state.shape[-1] != W:
+        raise KernelError("mingru: shape mismatch")
+    n_chunks, n_req = chunk_meta.shape[0], req_chunks.shape[0]
+    scratch = torch.empty((2, max(1, n_chunks), W), dtype=torch.float32, device=a.device)
+    check(_lib.load().mm_mingru_chunked(a.data_ptr(), y.data_ptr(), dtype_code(y.dtype), state.data_ptr(), scratch[0].data_ptr(),
+                                        scratch[1].data_ptr(), chunk_meta.data_ptr(), req_chunks.data_ptr(), slots.data_ptr(),
+                                        positions.data_ptr(), n_req, n_chunks, W, _stream()), "mingru_chunked")
+    return y
+
+
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}
+
+
+def bias_act(x: torch.Tensor, bias: Optional[torch.Tensor], activation: str, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = act(x + bias) in fp32 arithmetic; ``activation`` one of relu2 (squared relu), gelu_tanh, silu, relu."""
+    _need(x, "bias_act x")
+    if activation not in ACTIVATIONS:
+        raise KernelError(f"activation '{activation}' is not one of {', '.join(sorted(ACTIVATIONS))}")
+    out = torch.empty_like(x) if out is None else out
+    _need(out, "bias_act out", x.dtype)
+    n, f = x.shape
+    if bias is not None:
+        _need(bias, "bias_act bias")
+        if bias.shape != (f,):
+            raise KernelError("bias_act: bias shape mismatch")
+    check(_lib.load().mm_bias_act(x.data_ptr(), _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32, out.data_ptr(),
+                                  dtype_code(x.dtype), n, f, ACTIVATIONS[activation], _stream()), "bias_act")
+    return out

@@ -167,6 +167,15 @@ class ResidualSink:
 
 
 @dataclass
+class NormedRows:
+    """Rows that a block's first norm would produce, already made by the block before it (which added its last branch
+    into the residual stream and normed the sum in one launch): handed over as ``pending`` between blocks that agree
+    on it (``Block.entry_weights``)."""
+
+    x: torch.Tensor
+
+
+@dataclass
 class NativeDesc:
     """What the native step executor (csrc/exec) needs to build its own object of a part: the kind under which a
     C++ class is registered, numbers, tensors (as the part holds them after fusing) and the parts inside it."""
@@ -192,6 +201,21 @@ class Part:
         """The part's description for the native step executor, or None: the part exists in Python only, and a model
         that holds it runs its steps through the Python classes."""
         return None
+
+
+class Embedding(Part):
+    """Token ids to the first residual stream (fp32 [n_tokens, width])."""
+
+    def state_spec(self) -> Optional[StateSpec]:
+        """Fixed-size state per request (what the embedding must remember of a request's earlier steps), or None."""
+        return None
+
+    def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+    def embed(self, ctx: StepContext, state: Optional[torch.Tensor]) -> torch.Tensor:
+        """The step's rows; ``state`` is the embedding's ``[slots, *shape]`` array when it declares one."""
+        return self.forward(ctx.token_ids)
 
 
 class Norm(Part):

@@ -12,7 +12,7 @@ from typing import Optional
 import torch
 
 from ..registry import BLOCKS
-from .base import Block, FactoredRows, LayerCache, NativeDesc, ResidualSink, StepContext
+from .base import Block, FactoredRows, LayerCache, NativeDesc, NormedRows, ResidualSink, StepContext
 
 
 @BLOCKS.register("pre_norm")
@@ -66,3 +66,68 @@ class PreNormBlock(Block):
         if ctx.dump is not None:
             dump("l_out", residual + out.to(residual.dtype))
         return out
+
+
+@BLOCKS.register("sandwich_norm")
+class SandwichNormBlock(Block):
+    """A norm before and after each sublayer: ``x += post1(mixer(pre1(x)))``, then ``x += post2(ffn(pre2(x)))``; a layer
+    whose feed-forward is of kind ``none`` has the first sublayer only.  The two post norms are the layer's extra parts
+    ``mixer_post_norm`` and ``ffn_post_norm``.
+
+    The branch is normed, added into the fp32 residual stream and the sum normed for the next sublayer in one launch
+    where the two norms are grouped RMS norms of one shape; the last add of the layer does so for the first norm of
+    the block that follows and hands its rows over as ``NormedRows``.  The residual stream is complete when the block
+    returns."""
+
+    def __init__(self, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        from .mlp import NoFeedForward
+        self.has_ffn = not isinstance(self.feed_forward, NoFeedForward)
+        for name in ("mixer_post_norm",) + (("ffn_post_norm",) if self.has_ffn else ()):
+            if name not in self.extras:
+                raise ValueError(f"sandwich_norm block: the layer has no '{name}'")
+        self.mixer_post = self.extras["mixer_post_norm"]
+        self.ffn_post = self.extras.get("ffn_post_norm")
+
+    def accepts_normed_rows(self) -> bool:
+        """True if a predecessor may run this block's first norm for it."""
+        return hasattr(self.mixer_norm, "same_shape")
+
+    @staticmethod
+    def _add(post, residual: torch.Tensor, branch: torch.Tensor, then):
+        """residual += post(branch); returns then(residual) if ``then`` is given."""
+        if hasattr(post, "add_normed") and (then is None or hasattr(then, "same_shape")):
+            return post.add_normed(residual, branch, then)
+        zero = torch.zeros_like(residual)
+        normed = post.forward(zero, branch)                    # any other norm: through its plain interface
+        if then is None:
+            ops_add(residual, normed)
+            return None
+        return then.forward(residual, normed)
+
+    def forward(self, residual: torch.Tensor, pending, ctx: StepContext, cache: LayerCache,
+                successor: Optional[Block] = None):
+        dump = ctx.dump or (lambda stage, t: None)
+        h = pending.x if isinstance(pending, NormedRows) else self.mixer_norm.forward(residual, pending)
+        dump("attn_norm", h)
+        branch = self.mixer.forward(h, ctx, cache)
+        dump("attn_out", branch)
+        hand_over = None
+        if successor is not None and isinstance(successor, SandwichNormBlock) and successor.accepts_normed_rows() and not ctx.plain_only:
+            hand_over = successor.mixer_norm
+        if self.has_ffn:
+            h = self._add(self.mixer_post, residual, branch, self.ffn_norm)
+            branch = self.feed_forward.forward(h, ctx)
+            dump("ffn_mlp", branch)
+            post = self.ffn_post
+        else:
+            post = self.mixer_post
+        made = self._add(post, residual, branch, hand_over)
+        if ctx.dump is not None:
+            dump("l_out", residual)
+        return NormedRows(made) if made is not None else None
+
+
+def ops_add(residual: torch.Tensor, delta: torch.Tensor) -> None:
+    from ..kernels import ops
+    ops.add_residual(residual, delta)

@@ -8,19 +8,19 @@ computed only for the rows whose logits are wanted and returned as fp32.
 """
 from __future__ import annotations
 
-from typing import List
+from typing import List, Optional
 
 import torch
 
 from ..config.spec import PartSpec, TensorSpec
 from ..kernels import ops
 from ..registry import EMBEDDINGS, HEADS
-from .base import NativeDesc, Part, Runtime, WeightView
+from .base import Embedding, NativeDesc, Part, Runtime, StateSpec, StepContext, WeightView
 from .linear import linear
 
 
 @EMBEDDINGS.register("token_embedding")
-class TokenEmbedding(Part):
+class TokenEmbedding(Embedding):
     """spec params: vocab, width, scale, weight (full tensor name)."""
 
     @classmethod
@@ -42,6 +42,41 @@ class TokenEmbedding(Part):
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         out = torch.empty((token_ids.numel(), self.width), dtype=torch.float32, device=token_ids.device)
         return ops.embedding(token_ids, self.table, out, self.scale)
+
+
+@EMBEDDINGS.register("bigram_embedding")
+class BigramEmbedding(Embedding):
+    """Token row plus a hashed row for the pair (previous token, token):
+    ``x = E[id] + B[(prev * mul_prev + id * mul_cur) mod buckets]``, and the table's extra row ``buckets`` for a
+    sequence's first token.  The previous token of a portion's first token is per-request state (one int32).
+
+    spec params: vocab, width, buckets, mul_prev, mul_cur, weight, pairs (full tensor names)."""
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec, prefix: str) -> List[TensorSpec]:
+        return [TensorSpec(spec["weight"], (spec["vocab"], spec["width"]), role="table"),
+                TensorSpec(spec["pairs"], (spec["buckets"] + 1, spec["width"]), role="table")]
+
+    def __init__(self, spec: PartSpec, weights: WeightView, rt: Runtime):
+        super().__init__(spec, weights, rt)
+        self.vocab, self.width = int(spec["vocab"]), int(spec["width"])
+        self.buckets, self.mul_prev, self.mul_cur = int(spec["buckets"]), int(spec["mul_prev"]), int(spec["mul_cur"])
+        if self.buckets < 1:
+            raise ValueError("bigram embedding: buckets must be positive")
+        self.table = weights.get(spec["weight"]).contiguous()
+        self.pairs = weights.get(spec["pairs"]).contiguous()
+        if self.pairs.dtype != self.table.dtype:
+            self.table, self.pairs = self.table.float(), self.pairs.float()
+
+    def state_spec(self) -> Optional[StateSpec]:
+        return StateSpec((1,), torch.int32)
+
+    def embed(self, ctx: StepContext, state: Optional[torch.Tensor]) -> torch.Tensor:
+        if state is None:
+            raise RuntimeError("the bigram embedding needs its per-request state")
+        out = torch.empty((ctx.n_tokens, self.width), dtype=torch.float32, device=ctx.token_ids.device)
+        return ops.embedding_bigram(ctx.token_ids, ctx.positions, ctx.token_req, ctx.req_meta, ctx.state_slots, state, self.table,
+                                    self.pairs, out, self.buckets, self.mul_prev, self.mul_cur)
 
 
 @HEADS.register("lm_head")

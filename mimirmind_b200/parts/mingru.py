@@ -1,0 +1,77 @@
+"""minGRU mixer: a gated recurrence whose gates read only the current token.
+
+``z = sigmoid(h·W_zᵀ + b_z)``, ``u = h·W_xᵀ + b_x``, candidate ``c = u + 1/2`` where ``u ≥ 0`` and ``sigmoid(u)`` below;
+``S_t = (1 − z)·S_(t−1) + z·c`` element by element; output ``(S_t · silu(h·W_gᵀ))·W_oᵀ``.  The state starts at zero,
+is fp32 and is carried per request in the engine's state slots.  The three input projections are one product with an
+fp32 result; everything between it and the output projection is fp32 (``csrc/mingru.cu``).
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import numpy as np
+import torch
+
+from ..config.spec import PartSpec, TensorSpec
+from ..kernels import ops
+from ..registry import MIXERS
+from .base import LayerCache, Mixer, Runtime, StateSpec, StepContext, WeightView
+from .linear import linear
+
+CHUNK = 64               # tokens per chunk of the three-pass scan
+CHUNKED_FROM = 256       # a step whose longest portion has at least this many tokens takes the three-pass scan
+
+
+@MIXERS.register("mingru")
+class MinGRU(Mixer):
+    """spec params: hidden, width, and the tensor names z, x, g, o (weights), z_bias, x_bias."""
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec, prefix: str) -> List[TensorSpec]:
+        d, w = spec["hidden"], spec["width"]
+        return [TensorSpec(prefix + spec["z"], (w, d)), TensorSpec(prefix + spec["z_bias"], (w,), role="bias"),
+                TensorSpec(prefix + spec["x"], (w, d)), TensorSpec(prefix + spec["x_bias"], (w,), role="bias"),
+                TensorSpec(prefix + spec["g"], (w, d)), TensorSpec(prefix + spec["o"], (d, w))]
+
+    def __init__(self, spec: PartSpec, weights: WeightView, rt: Runtime):
+        super().__init__(spec, weights, rt)
+        self.hidden, self.width = int(spec["hidden"]), int(spec["width"])
+        ws = [weights.take(spec[n]) for n in ("z", "x", "g")]
+        if len({w.dtype for w in ws}) > 1:
+            ws = [w.float() for w in ws]
+        self.w_zxg = torch.cat(ws, dim=0).contiguous()
+        del ws
+        bz, bx = weights.take(spec["z_bias"]), weights.take(spec["x_bias"])
+        self.b_zxg = torch.cat([bz.float(), bx.float(), torch.zeros(self.width, dtype=torch.float32, device=bz.device)]).contiguous()
+        self.w_o = weights.take(spec["o"]).contiguous()
+
+    def state_spec(self) -> Optional[StateSpec]:
+        return StateSpec((self.width,), torch.float32)
+
+    @staticmethod
+    def _chunks(ctx: StepContext):
+        """The step's tokens cut into chunks, per request in order: (chunk_meta [chunks, 4], req_chunks [requests, 2])
+        on the device, made once per step."""
+        key = ("mingru_chunks", CHUNK)
+        if key not in ctx.derived:
+            meta, per_req = [], []
+            for r, (s, n) in enumerate(zip(ctx.q_start, ctx.q_len)):
+                first = len(meta)
+                for off in range(0, n, CHUNK):
+                    meta.append((s + off, min(CHUNK, n - off), r, int(off == 0)))
+                per_req.append((first, len(meta) - first))
+            host = np.concatenate([np.asarray(meta, dtype=np.int32).reshape(-1), np.asarray(per_req, dtype=np.int32).reshape(-1)])
+            dev = torch.from_numpy(host).to(ctx.token_ids.device)
+            ctx.derived[key] = (dev[:4 * len(meta)].view(len(meta), 4), dev[4 * len(meta):].view(len(per_req), 2))
+        return ctx.derived[key]
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
+        n = x.shape[0]
+        a = linear(x, self.w_zxg, self.b_zxg, self.rt, out_dtype=torch.float32)
+        y = torch.empty((n, self.width), dtype=self.rt.dtype, device=a.device)
+        if ctx.max_q_len >= CHUNKED_FROM:
+            chunk_meta, req_chunks = self._chunks(ctx)
+            ops.mingru_chunked(a, y, cache.state, chunk_meta, req_chunks, ctx.state_slots, ctx.positions)
+        else:
+            ops.mingru_walk(a, y, cache.state, ctx.req_meta, ctx.state_slots, ctx.positions, ctx.n_requests)
+        return linear(y, self.w_o, None, self.rt)

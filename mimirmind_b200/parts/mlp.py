@@ -83,3 +83,45 @@ class SwiGLU(FeedForward):
             act = torch.empty((m, self.intermediate), dtype=x.dtype, device=x.device)
             ops.silu_mul(gu, act, self.interleave)
         return linear(act, self.w_down, None, self.rt)
+
+
+@FEED_FORWARDS.register("dense_mlp")
+class DenseMLP(FeedForward):
+    """Two-matrix feed-forward ``y = act(x·W_upᵀ + b_up)·W_downᵀ + b_down`` with the activation as a parameter
+    (``relu2``: the square of relu; ``gelu_tanh``; ``silu``; ``relu``).  Bias and activation are one fp32 pass over the
+    hidden rows (``csrc/bias_act.cu``).
+
+    spec params: hidden, ff, activation, bias (bool), up, down (weights; biases are the name + ``bias_suffix``)."""
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec, prefix: str) -> List[TensorSpec]:
+        d, f = spec["hidden"], spec["ff"]
+        out = [TensorSpec(prefix + spec["up"], (f, d)), TensorSpec(prefix + spec["down"], (d, f))]
+        if spec.get("bias", False):
+            sfx = spec.get("bias_suffix", ".b")
+            out += [TensorSpec(prefix + spec["up"] + sfx, (f,), role="bias"), TensorSpec(prefix + spec["down"] + sfx, (d,), role="bias")]
+        return out
+
+    def __init__(self, spec: PartSpec, weights: WeightView, rt: Runtime):
+        super().__init__(spec, weights, rt)
+        self.hidden, self.ff = int(spec["hidden"]), int(spec["ff"])
+        self.activation = str(spec.get("activation", "relu2"))
+        if self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"dense_mlp: activation '{self.activation}' is not one of {', '.join(sorted(ops.ACTIVATIONS))}")
+        self.w_up = weights.take(spec["up"]).contiguous()
+        self.w_down = weights.take(spec["down"]).contiguous()
+        self.b_up = self.b_down = None
+        if spec.get("bias", False):
+            sfx = spec.get("bias_suffix", ".b")
+            self.b_up = weights.take(spec["up"] + sfx).contiguous()
+            self.b_down = weights.take(spec["down"] + sfx).contiguous()
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        hidden = linear(x, self.w_up, None, self.rt)
+        ops.bias_act(hidden, self.b_up, self.activation, hidden)
+        return linear(hidden, self.w_down, self.b_down, self.rt)
+
+
+@FEED_FORWARDS.register("none")
+class NoFeedForward(FeedForward):
+    """Stands where a layer has no feed-forward; the block arrangement skips the sublayer."""

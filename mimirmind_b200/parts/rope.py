@@ -43,3 +43,25 @@ class NoPositionEncoding(PositionEncoding):
 
     def native(self):
         return NativeDesc("none") if type(self) is NoPositionEncoding else None
+
+
+@POSITION_ENCODINGS.register("rotary_pairs")
+class RotaryPairs(PositionEncoding):
+    """Rotation of adjacent pairs: dimensions ``2i`` and ``2i+1`` (``i < dims/2``) of every head turn by
+    ``angle = pos * base^(-2i/dims)``: ``(u, v) -> (u cos - v sin, v cos + u sin)``; dimensions from ``dims`` on pass
+    unchanged.  The frequencies are made once in float64 and kept as an fp32 table; the angle is an fp32 product.
+
+    spec params: base, dims."""
+
+    def __init__(self, spec: PartSpec, weights: WeightView, rt: Runtime):
+        super().__init__(spec, weights, rt)
+        import torch
+        self.base, self.dims = float(spec["base"]), int(spec["dims"])
+        if self.dims % 2 or self.dims < 0:
+            raise ValueError("rotary_pairs: dims must be even")
+        i = torch.arange(max(1, self.dims // 2), dtype=torch.float64)
+        self.inv_freq = torch.pow(torch.tensor(self.base, dtype=torch.float64), -2.0 * i / max(1, self.dims)).to(torch.float32).to(rt.device)
+
+    def pair_rotation(self) -> Tuple[int, "object"]:
+        """(dims, fp32 frequency table) for kernels that rotate adjacent pairs themselves."""
+        return self.dims, self.inv_freq

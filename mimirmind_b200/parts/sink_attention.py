@@ -1,0 +1,110 @@
+"""Windowed self-attention with a softmax sink, keys and values of different sizes, and value mixing between layers.
+
+``q, k, v = h·Wᵀ + b`` with ``H`` query heads and ``G`` key/value heads (query head ``h`` reads key/value head
+``h // (H/G)``), keys of size ``key_dim`` and values of size ``value_dim``.  The position encoding turns q and k.
+``s = (q·k)·scale``; a query at position ``a`` sees keys ``max(0, a+1−W) .. a``; the weights are
+``exp(s_j) / (sink + Σ exp(s_i))`` with ``sink`` 1 (a key of score 0 without a value) or 0 (plain softmax).
+
+Value mixing (``v_mix``): the first layer of a model that names a mixing key is the *source*; every later layer of
+that key caches and uses ``(1 − λ)·v + λ·v_source`` of the same token, λ a scalar tensor of the layer.  The source's
+values of the step's tokens are handed on through the step context, so nothing of it is cached twice.
+
+Every size and constant is a parameter; the pools are per-token arrays ``k`` ``(G, key_dim)`` and ``v``
+``(G, value_dim)`` of the paged cache.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from ..config.spec import PartSpec, TensorSpec
+from ..kernels import ops
+from ..registry import MIXERS, POSITION_ENCODINGS
+from .base import CacheArray, KVCacheSpec, LayerCache, Mixer, Runtime, StepContext, WeightView
+from .linear import linear
+
+
+@MIXERS.register("sink_attention")
+class SinkAttention(Mixer):
+    """spec params: hidden, num_heads, num_kv_heads, key_dim, value_dim, window (0: all), scale, sink (bool), bias
+    (bool: q, k, v and o), position (PartSpec or None), v_mix (None, "source" or "mix"), v_mix_key, and the tensor
+    names q, k, v, o (weights; biases are the name + ``bias_suffix``) and mix (the scalar λ)."""
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec, prefix: str) -> List[TensorSpec]:
+        d, H, G, dk, dv = spec["hidden"], spec["num_heads"], spec["num_kv_heads"], spec["key_dim"], spec["value_dim"]
+        out = [TensorSpec(prefix + spec["q"], (H * dk, d)), TensorSpec(prefix + spec["k"], (G * dk, d)),
+               TensorSpec(prefix + spec["v"], (G * dv, d)), TensorSpec(prefix + spec["o"], (d, H * dv))]
+        if spec.get("bias", False):
+            sfx = spec.get("bias_suffix", ".b")
+            out += [TensorSpec(prefix + spec["q"] + sfx, (H * dk,), role="bias"), TensorSpec(prefix + spec["k"] + sfx, (G * dk,), role="bias"),
+                    TensorSpec(prefix + spec["v"] + sfx, (G * dv,), role="bias"), TensorSpec(prefix + spec["o"] + sfx, (d,), role="bias")]
+        if spec.get("v_mix"):
+            out.append(TensorSpec(prefix + spec["mix"], (), role="mix"))
+        return out
+
+    def __init__(self, spec: PartSpec, weights: WeightView, rt: Runtime):
+        super().__init__(spec, weights, rt)
+        self.hidden = int(spec["hidden"])
+        self.num_heads, self.num_kv_heads = int(spec["num_heads"]), int(spec["num_kv_heads"])
+        self.key_dim, self.value_dim = int(spec["key_dim"]), int(spec["value_dim"])
+        self.window = int(spec.get("window", 0) or 0)
+        self.scale = float(spec["scale"])
+        self.sink = bool(spec.get("sink", True))
+        if self.num_heads % self.num_kv_heads:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        pos_spec: Optional[PartSpec] = spec.get("position")
+        self.position = POSITION_ENCODINGS.get(pos_spec.kind)(pos_spec, weights, rt) if pos_spec is not None else None
+        if self.position is not None and not hasattr(self.position, "pair_rotation"):
+            raise ValueError(f"sink attention: the position encoding '{pos_spec.kind}' does not rotate adjacent pairs")
+        self.rot_dims, self.inv_freq = self.position.pair_rotation() if self.position is not None else (0, torch.zeros(1, device=rt.device))
+        if self.rot_dims > self.key_dim:
+            raise ValueError("sink attention: more rotated dimensions than the key size")
+        sfx = spec.get("bias_suffix", ".b")
+        ws = [weights.take(spec[n]) for n in ("q", "k", "v")]
+        if len({w.dtype for w in ws}) > 1:
+            ws = [w.float() for w in ws]
+        self.w_qkv = torch.cat(ws, dim=0).contiguous()
+        del ws
+        self.b_qkv = self.b_o = None
+        if spec.get("bias", False):
+            bs = [weights.take(spec[n] + sfx) for n in ("q", "k", "v")]
+            self.b_qkv = torch.cat([b.to(self.w_qkv.dtype) for b in bs], dim=0).contiguous()
+            self.b_o = weights.take(spec["o"] + sfx).contiguous()
+        self.w_o = weights.take(spec["o"]).contiguous()
+        self.v_mix = spec.get("v_mix") or None
+        if self.v_mix not in (None, "source", "mix"):
+            raise ValueError("sink attention: v_mix is None, 'source' or 'mix'")
+        self.v_mix_key = ("v_source", spec.get("v_mix_key", "v"))
+        self.mix = 0.0
+        if self.v_mix:
+            lam = weights.take(spec["mix"])
+            # read once at load: the kernel takes it by value (fp32)
+            self.mix = float(lam.float().item()) if self.v_mix == "mix" else 0.0
+
+    def kv_cache_spec(self) -> Optional[KVCacheSpec]:
+        return KVCacheSpec(self.num_kv_heads, self.key_dim, self.window,
+                           arrays=(CacheArray("k", (self.num_kv_heads, self.key_dim)), CacheArray("v", (self.num_kv_heads, self.value_dim))))
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
+        n = x.shape[0]
+        H, G, dk, dv = self.num_heads, self.num_kv_heads, self.key_dim, self.value_dim
+        k_pages, v_pages = (cache.arrays["k"], cache.arrays["v"]) if cache.writes else (None, None)
+        qkv = linear(x, self.w_qkv, self.b_qkv, self.rt)
+        q = torch.empty((n, H * dk), dtype=self.rt.dtype, device=qkv.device)
+        mode, v_first = 0, None
+        if self.v_mix == "source":
+            mode = 1
+            v_first = ctx.derived[self.v_mix_key] = torch.empty((n, G * dv), dtype=self.rt.dtype, device=qkv.device)
+        elif self.v_mix == "mix":
+            mode = 2
+            v_first = ctx.derived.get(self.v_mix_key)
+            if v_first is None:
+                raise RuntimeError("sink attention: a layer mixes values before any layer of its key has made them")
+        ops.qkv_pairs_post(qkv, q, k_pages, v_pages, v_first, self.inv_freq, ctx.positions, ctx.token_req, cache.block_table,
+                           cache.page_size, H, G, dk, dv, self.rot_dims, mode, self.mix)
+        out = torch.empty((n, H * dv), dtype=self.rt.dtype, device=qkv.device)
+        from ..kernels import attention as attn_kernels
+        attn_kernels.paged_sink_attention(q, cache, out, ctx, H, G, dk, dv, self.window, self.scale, self.sink)
+        return linear(out, self.w_o, self.b_o, self.rt)

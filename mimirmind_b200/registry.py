@@ -97,6 +97,16 @@ def get_architecture(name: str) -> ArchitectureEntry:
     return ARCHITECTURES.get(name)
 
 
+def architecture_name(config: Dict[str, Any]) -> str:
+    """The name a config.json chooses its model class by: the first of ``architectures`` (a list) or ``architecture``
+    (a string); empty when it has neither."""
+    archs = config.get("architectures")
+    if isinstance(archs, list) and archs and isinstance(archs[0], str):
+        return archs[0]
+    one = config.get("architecture")
+    return one if isinstance(one, str) else ""
+
+
 _builtin_loaded = False
 
 
@@ -107,4 +117,4 @@ def _ensure_builtin() -> None:
         return
     _builtin_loaded = True
     from . import parts  # noqa: F401  (registers part kinds)
-    from .models import qwen2  # noqa: F401  (registers the architecture)
+    from .models import bigerax, qwen2  # noqa: F401  (register the architectures)

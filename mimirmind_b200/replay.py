@@ -32,7 +32,7 @@ def main(argv=None) -> int:
     ps = args.page_size
     rounded = ((args.max_tokens + TOKEN_ROUNDING - 1) // TOKEN_ROUNDING) * TOKEN_ROUNDING
     num_pages = (rounded + ps - 1) // ps
-    runner = ModelRunner(model, page_size=ps, num_pages=num_pages, max_requests=MAX_LIVE * 2)
+    runner = ModelRunner(model, page_size=ps, num_pages=num_pages, max_requests=MAX_LIVE)
     os.makedirs(args.out, exist_ok=True)
     print(f"trace_run: ready, {num_pages} pages of {ps} tokens per cache group", file=sys.stderr, flush=True)
 

@@ -21,7 +21,7 @@ import torch
 
 from ..config.model_config import read_config_json
 from ..config.spec import ModelSpec, TensorSpec
-from ..registry import (EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, get_architecture, part_class)
+from ..registry import (EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, architecture_name, get_architecture, part_class)
 from .safetensors_io import SafetensorsFolder, write_safetensors
 
 
@@ -79,11 +79,11 @@ def _storage_dtype(t: torch.Tensor, run_dtype: torch.dtype) -> torch.dtype:
 def load_spec(model_dir: str):
     """(typed config, ModelSpec) of a model folder; the class is chosen by config.json."""
     obj = read_config_json(model_dir)
-    archs = obj.get("architectures")
-    if not (isinstance(archs, list) and archs and isinstance(archs[0], str)):
+    name = architecture_name(obj)
+    if not name:
         from ..config.model_config import ConfigError
         raise ConfigError(f"{model_dir}/config.json: missing 'architectures'")
-    entry = get_architecture(archs[0])
+    entry = get_architecture(name)
     cfg = entry.parse_config(obj, os.path.join(model_dir, "config.json"))
     return cfg, entry.build_spec(cfg)
 
@@ -108,6 +108,7 @@ def load_tensors(model_dir: str, spec: ModelSpec, run_dtype: torch.dtype, device
 MATRIX_STD = 0.02
 BIAS_STD = 0.02
 NORM_STD = 0.1
+MIX_STD = 0.15     # a mixing weight between two streams ~ 0.5 + N(0, 0.15), kept inside (0, 1)
 
 
 def _tensor_seed(seed: int, name: str) -> int:
@@ -130,6 +131,8 @@ def random_tensors(spec: ModelSpec, seed: int, dtype: torch.dtype, device="cpu")
             x = 1.0 + NORM_STD * x
         elif ts.role == "bias":
             x = BIAS_STD * x
+        elif ts.role == "mix":
+            x = (0.5 + MIX_STD * x).clamp(0.05, 0.95)
         else:
             x = MATRIX_STD * x
         out[name] = x.to(dtype)
@@ -152,8 +155,7 @@ def write_random_model(model_dir: str, config: Dict, seed: int, dtype: Optional[
 
     ``config`` is the config.json object of the architecture; ``dtype`` (default: its torch_dtype)
     is the stored precision."""
-    archs = config.get("architectures")
-    entry = get_architecture(archs[0] if isinstance(archs, list) and archs else "")
+    entry = get_architecture(architecture_name(config))
     config = dict(config)
     if dtype is not None:
         config["torch_dtype"] = {"fp32": "float32", "bf16": "bfloat16"}.get(dtype, dtype)
