@@ -103,7 +103,8 @@ class Engine:
         from ..registry import get_architecture
         entry = cfg.model(model_id)
         if entry.random:
-            arch = get_architecture(entry.random["config"]["architectures"][0])
+            from ..registry import architecture_name
+            arch = get_architecture(architecture_name(entry.random["config"]))
             spec = arch.build_spec(arch.parse_config(entry.random["config"], f"models[{entry.id}].random.config"))
             model = random_model(spec, int(entry.random.get("seed", 0)), cfg.runtime.dtype)
         else:

@@ -69,7 +69,8 @@ class MinGRU(Mixer):
         n = x.shape[0]
         a = linear(x, self.w_zxg, self.b_zxg, self.rt, out_dtype=torch.float32)
         y = torch.empty((n, self.width), dtype=self.rt.dtype, device=a.device)
-        if ctx.max_q_len >= CHUNKED_FROM:
+        # the 32-bit path keeps one order of operations whatever the cutting: it always walks
+        if ctx.max_q_len >= CHUNKED_FROM and self.rt.dtype != torch.float32:
             chunk_meta, req_chunks = self._chunks(ctx)
             ops.mingru_chunked(a, y, cache.state, chunk_meta, req_chunks, ctx.state_slots, ctx.positions)
         else:
