@@ -23,10 +23,72 @@ def paged_attention(q, cache, out, ctx, num_heads: int, num_kv_heads: int, head_
                                  cache.block_table, cache.page_size, num_heads, num_kv_heads, head_dim, window, scale)
 
 
+USE_SINK_MMA = True        # False: the sink attention always runs the fp32-arithmetic kernel (tests compare the two)
+SINK_PREFILL_MIN = 16      # shorter portions go token by token through the decode kernel
+SINK_TILE_ROWS = 64
+_sink_declared = False
+
+
+def _sink_lib():
+    global _sink_declared
+    from ctypes import c_float, c_int, c_void_p
+    from . import lib as _lib
+    if not _sink_declared:
+        P, I, F = c_void_p, c_int, c_float
+        _lib.declare("mm_attention_sink_supported", [I, I])
+        _lib.declare("mm_attention_sink_prefill_bf16", [P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, P])
+        _lib.declare("mm_attention_sink_decode_bf16", [P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P])
+        _sink_declared = True
+    return _lib.load()
+
+
+def sink_plan(ctx, n_tokens: int):
+    """The step's tokens sorted once, on the host, into prefill tiles (64 query tokens of one request; portions of at
+    least SINK_PREFILL_MIN tokens) and decode items (single tokens); every layer of the step reuses it.  Returns
+    (tiles [n, 4] or None, n_tiles, items [m] or None, n_items); items None with n_items > 0 means every token."""
+    key = ("sink_attention_plan",)
+    plan = ctx.plans.get(key)
+    if plan is None:
+        tiles, items = [], []
+        for r in range(ctx.n_requests):
+            s, n, kv = ctx.q_start[r], ctx.q_len[r], ctx.kv_len[r]
+            if n >= SINK_PREFILL_MIN:
+                for off in range(0, n, SINK_TILE_ROWS):
+                    tiles.append((r, s + off, min(SINK_TILE_ROWS, n - off), kv - n + off))
+            else:
+                items.extend(range(s, s + n))
+        tiles.sort(key=lambda tile: tile[3] + tile[2])
+        device = ctx.positions.device
+        d_tiles = torch.tensor(tiles, dtype=torch.int32, device=device) if tiles else None
+        d_items = None if len(items) == n_tokens or not items else torch.tensor(items, dtype=torch.int32, device=device)
+        plan = ctx.plans[key] = (d_tiles, len(tiles), d_items, len(items))
+    return plan
+
+
 def paged_sink_attention(q, cache, out, ctx, num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int, window: int,
                          scale: float, sink: bool) -> torch.Tensor:
     """Windowed attention with a softmax sink over pools of keys ``[pages, G, page, key_dim]`` and values
-    ``[pages, G, page, value_dim]``."""
-    return ops.attention_sink_generic(q, cache.arrays["k"], cache.arrays["v"], out, ctx.positions, ctx.token_req,
-                                      cache.block_table, cache.page_size, num_heads, num_kv_heads, key_dim, value_dim, window,
-                                      scale, sink)
+    ``[pages, G, page, value_dim]``.  bfloat16 with key and value sizes the tensor-core kernels are built for: a tiled
+    kernel for portions, a kernel that shares keys between the query heads of a KV head for single tokens; anything
+    else: the fp32-arithmetic kernel."""
+    k_pages, v_pages, table = cache.arrays["k"], cache.arrays["v"], cache.block_table
+    if (USE_SINK_MMA and q.dtype == torch.bfloat16 and scale > 0 and num_heads // num_kv_heads <= 16
+            and _sink_lib().mm_attention_sink_supported(key_dim, value_dim)):
+        from .lib import check
+        lib = _sink_lib()
+        tiles, n_tiles, items, n_items = sink_plan(ctx, q.shape[0])
+        stream = ops._stream()
+        if n_tiles:
+            check(lib.mm_attention_sink_prefill_bf16(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), tiles.data_ptr(),
+                                                     n_tiles, table.data_ptr(), table.shape[1], cache.page_size, num_heads, num_kv_heads,
+                                                     key_dim, value_dim, int(window), float(scale), int(bool(sink)), stream),
+                  "attention_sink_prefill_bf16")
+        if n_items:
+            check(lib.mm_attention_sink_decode_bf16(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(),
+                                                    items.data_ptr() if items is not None else None, n_items, ctx.positions.data_ptr(),
+                                                    ctx.token_req.data_ptr(), table.data_ptr(), table.shape[1], cache.page_size, num_heads,
+                                                    num_kv_heads, key_dim, value_dim, int(window), float(scale), int(bool(sink)), stream),
+                  "attention_sink_decode_bf16")
+        return out
+    return ops.attention_sink_generic(q, k_pages, v_pages, out, ctx.positions, ctx.token_req, table, cache.page_size, num_heads,
+                                      num_kv_heads, key_dim, value_dim, window, scale, sink)

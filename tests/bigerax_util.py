@@ -48,8 +48,16 @@ CONFIGS = {
         attention(6, 2, 10, 12, window=70, rot=(10, 10000.0), v_mix=True, ff=40),
         attention(6, 2, 10, 12, window=16, rot=(4, 10000.0), v_mix=True),
     ]),
+    # key and value sizes of the tensor-core attention kernels, keys wider and narrower than values, windows that are
+    # and are not multiples of a key tile, eight query heads on two kv heads
+    "S": config(200, 128, 2, 1e-6, 97, 5, 3, [
+        attention(4, 2, 32, 64, window=64, rot=(32, 10000.0), v_mix=True, ff=192),
+        attention(8, 2, 96, 32, window=45, rot=(64, 500000.0), v_mix=False, ff=128),
+        mingru(96),
+        attention(4, 2, 32, 64, window=130, rot=(16, 10000.0), v_mix=True),
+    ]),
 }
-LENGTHS = {"P": [1, 9, 77, 300], "Q": [5, 70, 280], "R": [2, 33, 150, 270]}
+LENGTHS = {"P": [1, 9, 77, 300], "Q": [5, 70, 280], "R": [2, 33, 150, 270], "S": [3, 64, 129, 290]}
 
 
 def tensor_shapes(cfg):

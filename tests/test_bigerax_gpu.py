@@ -122,9 +122,14 @@ def _paged(k, v, page_size, rng, dtype):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,G,dk,dv,window,page", [(4, 2, 24, 16, 19, 16), (3, 3, 9, 7, 40, 8), (8, 1, 64, 64, 0, 16), (4, 4, 96, 32, 33, 32),
-                                                   (2, 1, 128, 128, 130, 16), (2, 2, 16, 200, 5, 16)])
-def test_sink_attention_against_the_plain_one(H, G, dk, dv, window, page, dtype):
+                                                   (2, 1, 128, 128, 130, 16), (2, 2, 16, 200, 5, 16), (16, 1, 32, 96, 100, 16),
+                                                   (6, 2, 128, 64, 0, 64)])
+@pytest.mark.parametrize("tensor_cores", [True, False])
+def test_sink_attention_against_the_plain_one(H, G, dk, dv, window, page, dtype, tensor_cores, monkeypatch):
     from mimirmind_b200.kernels import attention
+    if dtype == "float32" and not tensor_cores:
+        pytest.skip("the 32-bit path has one kernel")
+    monkeypatch.setattr(attention, "USE_SINK_MMA", tensor_cores)
     from mimirmind_b200.parts.base import LayerCache
     rng = np.random.RandomState(H * 100 + dk)
     T, scale = 300, 0.37 / np.sqrt(dk) * 4
@@ -168,15 +173,16 @@ def test_sink_attention_against_the_plain_one(H, G, dk, dv, window, page, dtype)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("window,page", [(40, 16), (64, 16), (17, 8), (0, 16)])
-def test_one_key_that_stands_out_is_seen_exactly_inside_the_window(window, page, dtype):
+@pytest.mark.parametrize("window,page", [(40, 16), (64, 16), (17, 8), (0, 16), (65, 32)])
+@pytest.mark.parametrize("dv", [8, 32])
+def test_one_key_that_stands_out_is_seen_exactly_inside_the_window(window, page, dtype, dv):
     """Every key is orthogonal to the query but one, whose score stands out by far and whose value is a marker: the
     output shows the marker exactly when that key is inside the window, in a prompt and for a single decoded token, with
     the key at a page's border, far back, and just inside and just outside the window."""
     from mimirmind_b200.kernels import attention
     from mimirmind_b200.parts.base import LayerCache
-    H = G = 2
-    dk, dv, T = 32, 8, 400
+    H, G = 4, 2                     # values of 8 run the fp32-arithmetic kernel, of 32 the tensor-core kernels (bfloat16)
+    dk, T = 32, 400
     rng = np.random.RandomState(window + page)
 
     class Ctx:
@@ -184,7 +190,7 @@ def test_one_key_that_stands_out_is_seen_exactly_inside_the_window(window, page,
 
     for query in (399, 256, 255, 64, 40, 17, 16, 1, 0):
         spots = {query, query - 1, 0, 15, 16, 17, query - window + 1, query - window, query - window - 1, (query // page) * page,
-                 (query // page) * page - 1, query - 200}
+                 (query // page) * page - 1, query - 200, (query // 64) * 64, (query // 64) * 64 - 1}
         for spot in sorted(s for s in spots if 0 <= s <= query):
             k = rng.randn(T, G, dk) * 0.01
             k[:, :, 0] = 0.0
@@ -342,7 +348,7 @@ def check_rows(trace, outputs, reqs, ref, dtype, what):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name,page_size", [("P", 16), ("Q", 16), ("R", 8), ("P", 32)])
+@pytest.mark.parametrize("name,page_size", [("P", 16), ("Q", 16), ("R", 8), ("P", 32), ("S", 16)])
 def test_every_way_of_cutting_matches_the_plain_implementation(name, page_size, dtype, models):
     folder, cfg, w = models(name)
     reqs = {f"{name}{i}": random_tokens(cfg["vocab"], n, 100 * i + n) for i, n in enumerate(bu.LENGTHS[name])}
