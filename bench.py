@@ -166,6 +166,146 @@ def run_workload(name: str, layers: int) -> int:
     return 0 if verified else 1
 
 
+# ---- another design beside the closest existing one, at equal size (--compare bigerax) ---------------------------------------
+# Layer sizes that resemble a real model's; both models get the same width, heads, key size, window, layer count and
+# vocabulary, and feed-forwards of equal parameter count (two matrices of ff against three of 2/3 ff).
+COMPARE_SIZES = {
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=64, window=1024, ff=8192, gru=2048, vocab=32768, layers=8),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, window=4096, ff=16384, gru=4096, vocab=65536, layers=8),
+}
+
+
+def bigerax_config(z):
+    att = {"type": "attention", "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"],
+                                          "scale": z["dim"] ** -0.5, "mask": {"size": z["window"]}, "rot": {"dims": z["dim"], "base": 500000.0},
+                                          "v_mix": True}, "mlp": {"kind": "dense", "ff": z["ff"]}}
+    gru = {"type": "mingru", "mixer": {"width": z["gru"]}, "mlp": None}
+    layers = [gru if i % 4 == 3 else att for i in range(z["layers"])]
+    return {"architecture": "Bigerax", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6, "groups": 2},
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}}, "layers": layers}
+
+
+def qwen2_config(z, context):
+    inter = -(-(2 * z["ff"] // 3) // 64) * 64
+    return dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=z["layers"], hidden_size=z["width"],
+                num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"], head_dim=z["dim"], intermediate_size=inter,
+                vocab_size=z["vocab"], rope_theta=500000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=context,
+                use_sliding_window=True, sliding_window=z["window"], max_window_layers=0, torch_dtype="bfloat16")
+
+
+def run_compare(args) -> int:
+    """Prefill and decode throughput of the Bigerax design beside the Qwen2 decoder at equal size (random weights, bfloat16):
+    one prompt in one step (median of five), and the captured decode step at the given batch over prompts of that length."""
+    import numpy as np
+    import torch
+    from mimirmind_b200.engine.decode_graph import decode_session
+    from mimirmind_b200.engine.engine import Engine
+    from mimirmind_b200.engine.loader import random_model
+    from mimirmind_b200.engine.runner import StepEntry
+    from mimirmind_b200.kernels import lib as kernel_lib
+    from mimirmind_b200.registry import architecture_name, get_architecture
+
+    torch.cuda.set_device(0)
+    kernel_lib.load(verbose=True)
+    prompt_len = args.prompt_len or PROMPT_LEN
+    steps, warmup, batch = max(1, min(args.steps, 128)), max(3, args.warmup), max(1, args.batch)
+    context = -(-(prompt_len + SETTLE_STEPS + warmup + steps + 1) // 1024) * 1024
+    out = {"compare": "bigerax", "beside": "qwen2", "dtype": "bf16", "data": "synthetic", "prompt_len": prompt_len, "batch": batch,
+           "steps": steps, "warmup": warmup, "sizes": {}}
+    sizes = [args.size] if args.size else sorted(COMPARE_SIZES)
+    for name in sizes:
+        z = dict(COMPARE_SIZES[name])
+        if args.layers:
+            z["layers"] = args.layers
+        row = {}
+        for which, cfg_json in (("bigerax", bigerax_config(z)), ("qwen2", qwen2_config(z, context))):
+            arch = get_architecture(architecture_name(cfg_json))
+            spec = arch.build_spec(arch.parse_config(cfg_json, "bench"))
+            model = random_model(spec, seed=0, dtype="bfloat16")
+            engine = Engine(model, page_size=PAGE_SIZE, cache_tokens=(batch + 1) * context, max_context=context,
+                            token_budget=prompt_len, max_active=batch + 1)
+            runner = engine.runner
+            rng = np.random.RandomState(0)
+            prompts = [rng.randint(0, z["vocab"], size=prompt_len).tolist() for _ in range(max(batch, 5))]
+
+            def prefill_once(rid, toks):
+                runner.add_request(rid)
+                return runner.step([StepEntry(rid, toks, [len(toks) - 1])])
+
+            for i in range(3):
+                prefill_once(("warm", i), prompts[i])
+                runner.release(("warm", i))
+            times = []
+            for i in range(5):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                a.record()
+                prefill_once(("pf", i), prompts[i])
+                b.record()
+                torch.cuda.synchronize()
+                times.append(a.elapsed_time(b))
+                runner.release(("pf", i))
+            pf_ms = sorted(times)[2]
+            ids, firsts = [("dec", i) for i in range(batch)], []
+            for rid, toks in zip(ids, prompts[:batch]):
+                firsts.append(int(prefill_once(rid, toks).argmax(-1).item()))
+            sess = decode_session(runner, batch, context, greedy=True, feed_back=True)
+            sess.bind(ids, SETTLE_STEPS + warmup + steps, firsts)
+            before = kernel_lib.launch_count()
+            sess.step()
+            launches = (kernel_lib.launch_count() - before) // 2
+            for _ in range(SETTLE_STEPS - 1 + warmup):
+                sess.step()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(steps):
+                sess.step()
+            b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / steps
+            params = sum(t.numel() for t in model_tensors(model))
+            row[which] = {"prefill_ms": pf_ms, "prefill_tokens_per_s": prompt_len / (pf_ms * 1e-3), "decode_ms_per_step": ms,
+                          "decode_tokens_per_s": batch / (ms * 1e-3), "launches_per_decode_step": launches, "parameters": params,
+                          "steps_in": "library executor" if runner.native is not None else "python parts (decode captured in a CUDA graph)"}
+            for r in ids:
+                runner.release(r)
+            del sess, engine, runner, model
+            torch.cuda.empty_cache()
+        row["prefill_ratio"] = row["bigerax"]["prefill_tokens_per_s"] / row["qwen2"]["prefill_tokens_per_s"]
+        row["decode_ratio"] = row["bigerax"]["decode_tokens_per_s"] / row["qwen2"]["decode_tokens_per_s"]
+        row["shape"] = z
+        out["sizes"][name] = row
+    print(json.dumps(out))
+    return 0
+
+
+def model_tensors(model):
+    """Every weight tensor the model's parts hold (for a parameter count)."""
+    import torch
+    seen, out = set(), []
+
+    def walk(obj, depth=0):
+        if depth > 3 or id(obj) in seen:
+            return
+        seen.add(id(obj))
+        for v in vars(obj).values() if hasattr(obj, "__dict__") else ():
+            if isinstance(v, torch.Tensor):
+                if v.is_floating_point() and v.data_ptr() not in seen:
+                    seen.add(v.data_ptr())
+                    out.append(v)
+            elif isinstance(v, dict):
+                for x in v.values():
+                    if hasattr(x, "__dict__"):
+                        walk(x, depth + 1)
+            elif hasattr(v, "__dict__") and v.__class__.__module__.startswith("mimirmind_b200.parts"):
+                walk(v, depth + 1)
+
+    for part in [model.embedding, model.head, model.final_norm] + list(model.layers):
+        walk(part)
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -189,8 +329,17 @@ def main() -> int:
                     help="with --only decode or prefill: prompts of this many tokens instead of 2,048 (the context grows with them)")
     ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE",
                     help="set a tunable of the library's dispatch (csrc/exec/exec.h, Options) for this run, e.g. cluster_max_wanted=64")
+    ap.add_argument("--compare", default="", choices=["", "bigerax"],
+                    help="instead of the default run: prefill and decode throughput of that design beside the Qwen2 decoder at equal "
+                         "size, at layer sizes that resemble a real model's (random weights; --size, --layers, --batch, --prompt-len, --steps)")
+    ap.add_argument("--size", default="", choices=[""] + sorted(COMPARE_SIZES), help="with --compare: one size only")
     args = ap.parse_args()
 
+    if args.compare and args.impl != "reference":
+        if args.gpus != 1:
+            print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+            return 2
+        return run_compare(args)
     if args.impl == "reference":
         # The attempt is on record (baseline/reference_arm.py is what drove it): the reference's binary builds offline with
         # its CUDA backend, loads a bfloat16 GGUF of this shape, and its process ends with SIGSEGV in generate() on this GPU,
