@@ -43,6 +43,24 @@ __global__ void embedding_bigram_kernel(const int32_t* __restrict__ ids, const i
     }
     const T* e = table + (size_t)id * d;
     const T* b = pairs + (size_t)row * d;
+    if (sizeof(T) == 2 && d % 8 == 0 && (((uintptr_t)table | (uintptr_t)pairs | (uintptr_t)out) & 15) == 0) {
+        // bfloat16 rows of a multiple of 8: one 16-byte load of each table and two 16-byte stores per thread and step
+        for (int i = threadIdx.x * 8; i < d; i += blockDim.x * 8) {
+            const uint4 ra = *reinterpret_cast<const uint4*>(e + i), rb = *reinterpret_cast<const uint4*>(b + i);
+            const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&ra);
+            const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&rb);
+            float f[8];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 x = __bfloat1622float2(a2[k]), y = __bfloat1622float2(b2[k]);
+                f[2 * k] = x.x + y.x;
+                f[2 * k + 1] = x.y + y.y;
+            }
+            *reinterpret_cast<float4*>(o + i) = make_float4(f[0], f[1], f[2], f[3]);
+            *reinterpret_cast<float4*>(o + i + 4) = make_float4(f[4], f[5], f[6], f[7]);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = to_f32<T>(e[i]) + to_f32<T>(b[i]);
 }
 

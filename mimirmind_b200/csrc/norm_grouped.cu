@@ -104,6 +104,84 @@ __global__ void group_norm_rows_kernel(const T* __restrict__ x, const WT* __rest
     for (int k = threadIdx.x; k < d; k += blockDim.x) out[i * d + k] = from_f32<T>(row[k] * inv[k / gs] * to_f32<WT>(w[k]));
 }
 
+// bfloat16 activations, width a multiple of 256 per group and at most 8192: a thread keeps 8 consecutive elements of the
+// row in registers (16-byte loads and stores), a warp's 256 elements lie in one group, and a group's sum is the sum of
+// its warps' partial sums in warp order.  One trip over the row for both norms.
+template <typename WT>
+__device__ __forceinline__ void load_weight8(const WT* __restrict__ w, float* f);
+template <>
+__device__ __forceinline__ void load_weight8<float>(const float* __restrict__ w, float* f) {
+    const float4 a = *reinterpret_cast<const float4*>(w), b = *reinterpret_cast<const float4*>(w + 4);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load_weight8<__nv_bfloat16>(const __nv_bfloat16* __restrict__ w, float* f) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(w);
+    const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float2 x = __bfloat1622float2(p2[k]);
+        f[2 * k] = x.x;
+        f[2 * k + 1] = x.y;
+    }
+}
+
+__device__ __forceinline__ float group_inv_rms8(const float* v, int warps_per_group, int gs, float eps, float* part) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float ss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) ss = fmaf(v[k], v[k], ss);
+    ss = warp_sum(ss);
+    __syncthreads();                      // part may still be read from an earlier call
+    if (lane == 0) part[warp] = ss;
+    __syncthreads();
+    const int first = (warp / warps_per_group) * warps_per_group;
+    float t = 0.0f;
+    for (int w = 0; w < warps_per_group; ++w) t += part[first + w];
+    return 1.0f / sqrtf(t / (float)gs + eps);
+}
+
+template <typename WT>
+__global__ void group_norm_chain_bf16x8_kernel(float* __restrict__ residual, const __nv_bfloat16* __restrict__ branch,
+                                               const WT* __restrict__ w_post, const WT* __restrict__ w_next,
+                                               const int32_t* __restrict__ rows, __nv_bfloat16* __restrict__ out, int d,
+                                               int groups, float eps) {
+    __shared__ float part[32];
+    const int i = blockIdx.x;
+    const size_t r = rows ? (size_t)rows[i] : (size_t)i;
+    const int c = threadIdx.x * 8;
+    const int gs = d / groups, wpg = gs / 256;
+    float v[8], w[8];
+    {
+        const float4 a = *reinterpret_cast<const float4*>(residual + r * d + c);
+        const float4 b = *reinterpret_cast<const float4*>(residual + r * d + c + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+    if (branch != nullptr) {
+        float bv[8];
+        load_weight8<__nv_bfloat16>(branch + r * d + c, bv);
+        if (w_post != nullptr) {
+            const float inv = group_inv_rms8(bv, wpg, gs, eps, part);
+            load_weight8<WT>(w_post + c, w);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[k] += bv[k] * inv * w[k];
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[k] += bv[k];
+        }
+        *reinterpret_cast<float4*>(residual + r * d + c) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(residual + r * d + c + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+    if (w_next == nullptr) return;
+    const float inv = group_inv_rms8(v, wpg, gs, eps, part);
+    load_weight8<WT>(w_next + c, w);
+    uint4 res;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&res);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) o2[k] = __floats2bfloat162_rn(v[2 * k] * inv * w[2 * k], v[2 * k + 1] * inv * w[2 * k + 1]);
+    *reinterpret_cast<uint4*>(out + (size_t)i * d + c) = res;
+}
+
 template <typename T, typename WT>
 static int launch_chain(float* residual, const void* branch, const void* w_post, const void* w_next, const int32_t* rows,
                         void* out, int n, int d, int groups, float eps, cudaStream_t s) {
@@ -133,6 +211,17 @@ MM_EXPORT int mm_group_norm_chain(void* residual, const void* branch, const void
     cudaStream_t s = (cudaStream_t)stream;
     float* res = (float*)residual;
     const int32_t* rw = (const int32_t*)rows;
+    if (dtype == MM_BF16 && (d / groups) % 256 == 0 && d <= 8192 &&
+        (((uintptr_t)residual | (uintptr_t)branch | (uintptr_t)w_post | (uintptr_t)w_next | (uintptr_t)out) & 15) == 0) {
+        if (weight_dtype == MM_BF16)
+            mm_launch(group_norm_chain_bf16x8_kernel<__nv_bfloat16>, dim3(n_out), dim3(d / 8), 0, s, res, (const __nv_bfloat16*)branch,
+                      (const __nv_bfloat16*)w_post, (const __nv_bfloat16*)w_next, rw, (__nv_bfloat16*)out, d, groups, eps);
+        else
+            mm_launch(group_norm_chain_bf16x8_kernel<float>, dim3(n_out), dim3(d / 8), 0, s, res, (const __nv_bfloat16*)branch,
+                      (const float*)w_post, (const float*)w_next, rw, (__nv_bfloat16*)out, d, groups, eps);
+        MM_CHECK_LAUNCH();
+        return MM_OK;
+    }
     if (dtype == MM_F32 && weight_dtype == MM_F32)
         return launch_chain<float, float>(res, branch, w_post, w_next, rw, out, n_out, d, groups, eps, s);
     if (dtype == MM_BF16 && weight_dtype == MM_BF16)

@@ -54,10 +54,11 @@ _PROTOTYPES = {
     "mm_group_norm_chain": [P, P, P, P, I, P, P, I, I, I, I, F, P],
     "mm_group_norm_rows": [P, P, I, P, I, I, I, I, F, P],
     "mm_embedding_bigram": [P, P, P, P, P, P, P, P, I, P, I, I, I, I, c_longlong, c_longlong, P],
-    "mm_qkv_pairs_post": [P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P],
+    "mm_qkv_pairs_post": [P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, F, P],
+    "mm_rope_pairs_table": [P, P, P, I, I, P],
     "mm_attention_sink_generic": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
-    "mm_mingru_walk": [P, P, I, P, P, P, P, I, I, P],
-    "mm_mingru_chunked": [P, P, I, P, P, P, P, P, P, P, I, I, I, P],
+    "mm_mingru_walk": [P, P, I, P, P, P, P, P, I, I, P],
+    "mm_mingru_chunked": [P, P, I, P, P, P, P, P, P, P, P, I, I, I, P],
     "mm_bias_act": [P, P, I, P, I, I, I, I, P],
 }
 

@@ -675,13 +675,25 @@ def embedding_bigram(ids: torch.Tensor, positions: torch.Tensor, token_req: torc
     return out
 
 
+def rope_pairs_table(positions: torch.Tensor, inv_freq: torch.Tensor, rot_dims: int) -> torch.Tensor:
+    """[n, rot_dims / 2, 2] fp32: (cos, sin) of position * inv_freq[i] for every token and pair of rotated dimensions."""
+    _need(positions, "positions", torch.int32)
+    _need(inv_freq, "inv_freq", torch.float32)
+    half = rot_dims // 2
+    if half < 1 or inv_freq.numel() < half:
+        raise KernelError("rope pairs table: bad sizes")
+    n = positions.numel()
+    out = torch.empty((n, half, 2), dtype=torch.float32, device=positions.device)
+    check(_lib.load().mm_rope_pairs_table(positions.data_ptr(), inv_freq.data_ptr(), out.data_ptr(), n, half, _stream()), "rope_pairs_table")
+    return out
+
+
 def qkv_pairs_post(qkv: torch.Tensor, q_out: torch.Tensor, k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
-                   v_first: Optional[torch.Tensor], inv_freq: torch.Tensor, positions: torch.Tensor, token_req: torch.Tensor,
-                   block_table: torch.Tensor, page_size: int, num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int,
-                   rot_dims: int, mix_mode: int, mix: float) -> None:
-    """Rotates adjacent pairs of q and k by position (angle = position * inv_freq[i], fp32), mixes the values
+                   v_first: Optional[torch.Tensor], rot: Optional[torch.Tensor], slots: Optional[torch.Tensor], page_size: int,
+                   num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int, rot_dims: int, mix_mode: int, mix: float) -> None:
+    """Rotates adjacent pairs of q and k by the angles of ``rot`` (:func:`rope_pairs_table`), mixes the values
     (mode 1: copy them to ``v_first``; 2: v = (1 - mix) v + mix v_first), writes q to ``q_out`` and k and the mixed v
-    into their pages ([pages, kv heads, page, key_dim] and [.., value_dim])."""
+    into their pages ([pages, kv heads, page, key_dim] and [.., value_dim]) at ``slots`` (:func:`slot_mapping`)."""
     _need(qkv, "qkv")
     n = qkv.shape[0]
     H, G, dk, dv = num_heads, num_kv_heads, key_dim, value_dim
@@ -695,20 +707,20 @@ def qkv_pairs_post(qkv: torch.Tensor, q_out: torch.Tensor, k_pages: Optional[tor
         _need(v_pages, "v_pages", qkv.dtype)
         if k_pages.shape[1:] != (G, page_size, dk) or v_pages.shape[1:] != (G, page_size, dv) or k_pages.shape[0] != v_pages.shape[0]:
             raise KernelError("qkv post: page pool shape mismatch")
+        _need(slots, "slots", torch.int32)
+        if slots.shape != (n,):
+            raise KernelError("slots: wrong shape")
     if mix_mode:
         _need(v_first, "v_first", qkv.dtype)
         if v_first.shape != (n, G * dv):
             raise KernelError("v_first: wrong shape")
-    _need(inv_freq, "inv_freq", torch.float32)
-    if inv_freq.numel() < rot_dims // 2:
-        raise KernelError("inv_freq: too short")
-    _need(positions, "positions", torch.int32)
-    _need(token_req, "token_req", torch.int32)
-    _need(block_table, "block_table", torch.int32)
+    if rot_dims:
+        _need(rot, "rotation table", torch.float32)
+        if rot.shape != (n, rot_dims // 2, 2):
+            raise KernelError("rotation table: wrong shape")
     check(_lib.load().mm_qkv_pairs_post(qkv.data_ptr(), q_out.data_ptr(), _ptr(k_pages), _ptr(v_pages), _ptr(v_first) if mix_mode else None,
-                                        dtype_code(qkv.dtype), inv_freq.data_ptr(), positions.data_ptr(), token_req.data_ptr(),
-                                        block_table.data_ptr(), block_table.shape[1], page_size, n, H, G, dk, dv, int(rot_dims),
-                                        int(mix_mode), float(mix), _stream()), "qkv_pairs_post")
+                                        dtype_code(qkv.dtype), _ptr(rot) if rot_dims else None, _ptr(slots) if k_pages is not None else None,
+                                        page_size, n, H, G, dk, dv, int(rot_dims), int(mix_mode), float(mix), _stream()), "qkv_pairs_post")
 
 
 def attention_sink_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor, positions: torch.Tensor,
@@ -736,10 +748,10 @@ def attention_sink_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
 
 
 def mingru_walk(a: torch.Tensor, y: torch.Tensor, state: torch.Tensor, req_meta: Optional[torch.Tensor], slots: torch.Tensor,
-                positions: torch.Tensor, n_requests: int) -> torch.Tensor:
+                positions: torch.Tensor, n_requests: int, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """minGRU over each request's tokens in order, one thread per (request, channel): ``a`` [n, 3W] fp32 holds the
-    projections for the gate, the candidate and the output gate; ``state`` [slots, W] fp32 is read and left updated;
-    ``y`` [n, W] gets state * silu(output gate)."""
+    projections for the gate, the candidate and the output gate (``bias`` [2W] fp32: the gate's and the candidate's, added
+    here); ``state`` [slots, W] fp32 is read and left updated; ``y`` [n, W] gets state * silu(output gate)."""
     _need(a, "mingru projections", torch.float32)
     _need(y, "mingru out")
     _need(state, "mingru state", torch.float32)
@@ -751,13 +763,21 @@ def mingru_walk(a: torch.Tensor, y: torch.Tensor, state: torch.Tensor, req_meta:
         raise KernelError("mingru: shape mismatch")
     if req_meta is not None:
         _need(req_meta, "req_meta", torch.int32)
+    _check_mingru_bias(bias, W)
     check(_lib.load().mm_mingru_walk(a.data_ptr(), y.data_ptr(), dtype_code(y.dtype), state.data_ptr(), _ptr(req_meta), slots.data_ptr(),
-                                     positions.data_ptr(), int(n_requests), W, _stream()), "mingru_walk")
+                                     positions.data_ptr(), _ptr(bias), int(n_requests), W, _stream()), "mingru_walk")
     return y
 
 
+def _check_mingru_bias(bias: Optional[torch.Tensor], W: int) -> None:
+    if bias is not None:
+        _need(bias, "mingru bias", torch.float32)
+        if bias.numel() != 2 * W:
+            raise KernelError("mingru: the bias holds the gate's and the candidate's, [2W]")
+
+
 def mingru_chunked(a: torch.Tensor, y: torch.Tensor, state: torch.Tensor, chunk_meta: torch.Tensor, req_chunks: torch.Tensor,
-                   slots: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+                   slots: torch.Tensor, positions: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """minGRU as a scan over chunks of tokens (three launches: every chunk from a zero state, the carry along each
     request's chunks, every chunk again from its starting state).  ``chunk_meta`` [chunks, 4] = (first token, tokens,
     request, .), ``req_chunks`` [requests, 2] = (first chunk, chunks)."""
@@ -772,11 +792,12 @@ def mingru_chunked(a: torch.Tensor, y: torch.Tensor, state: torch.Tensor, chunk_
     W = w3 // 3
     if w3 != 3 * W or y.shape != (n, W) or state.shape[-1] != W:
         raise KernelError("mingru: shape mismatch")
+    _check_mingru_bias(bias, W)
     n_chunks, n_req = chunk_meta.shape[0], req_chunks.shape[0]
     scratch = torch.empty((2, max(1, n_chunks), W), dtype=torch.float32, device=a.device)
     check(_lib.load().mm_mingru_chunked(a.data_ptr(), y.data_ptr(), dtype_code(y.dtype), state.data_ptr(), scratch[0].data_ptr(),
                                         scratch[1].data_ptr(), chunk_meta.data_ptr(), req_chunks.data_ptr(), slots.data_ptr(),
-                                        positions.data_ptr(), n_req, n_chunks, W, _stream()), "mingru_chunked")
+                                        positions.data_ptr(), _ptr(bias), n_req, n_chunks, W, _stream()), "mingru_chunked")
     return y
 
 

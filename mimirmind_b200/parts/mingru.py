@@ -42,7 +42,7 @@ class MinGRU(Mixer):
         self.w_zxg = torch.cat(ws, dim=0).contiguous()
         del ws
         bz, bx = weights.take(spec["z_bias"]), weights.take(spec["x_bias"])
-        self.b_zxg = torch.cat([bz.float(), bx.float(), torch.zeros(self.width, dtype=torch.float32, device=bz.device)]).contiguous()
+        self.b_zx = torch.cat([bz.float(), bx.float()]).contiguous()       # added inside the scan kernels, in fp32
         self.w_o = weights.take(spec["o"]).contiguous()
 
     def state_spec(self) -> Optional[StateSpec]:
@@ -67,12 +67,12 @@ class MinGRU(Mixer):
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
         n = x.shape[0]
-        a = linear(x, self.w_zxg, self.b_zxg, self.rt, out_dtype=torch.float32)
+        a = linear(x, self.w_zxg, None, self.rt, out_dtype=torch.float32)
         y = torch.empty((n, self.width), dtype=self.rt.dtype, device=a.device)
         # the 32-bit path keeps one order of operations whatever the cutting: it always walks
         if ctx.max_q_len >= CHUNKED_FROM and self.rt.dtype != torch.float32:
             chunk_meta, req_chunks = self._chunks(ctx)
-            ops.mingru_chunked(a, y, cache.state, chunk_meta, req_chunks, ctx.state_slots, ctx.positions)
+            ops.mingru_chunked(a, y, cache.state, chunk_meta, req_chunks, ctx.state_slots, ctx.positions, self.b_zx)
         else:
-            ops.mingru_walk(a, y, cache.state, ctx.req_meta, ctx.state_slots, ctx.positions, ctx.n_requests)
+            ops.mingru_walk(a, y, cache.state, ctx.req_meta, ctx.state_slots, ctx.positions, ctx.n_requests, self.b_zx)
         return linear(y, self.w_o, None, self.rt)

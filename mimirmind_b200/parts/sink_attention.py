@@ -58,7 +58,8 @@ class SinkAttention(Mixer):
         self.position = POSITION_ENCODINGS.get(pos_spec.kind)(pos_spec, weights, rt) if pos_spec is not None else None
         if self.position is not None and not hasattr(self.position, "pair_rotation"):
             raise ValueError(f"sink attention: the position encoding '{pos_spec.kind}' does not rotate adjacent pairs")
-        self.rot_dims, self.inv_freq = self.position.pair_rotation() if self.position is not None else (0, torch.zeros(1, device=rt.device))
+        self.rot_dims, self.inv_freq = self.position.pair_rotation() if self.position is not None else (0, None)
+        self.rot_key = ("rope_pairs", self.rot_dims, float(pos_spec["base"])) if self.rot_dims else None
         if self.rot_dims > self.key_dim:
             raise ValueError("sink attention: more rotated dimensions than the key size")
         sfx = spec.get("bias_suffix", ".b")
@@ -102,8 +103,18 @@ class SinkAttention(Mixer):
             v_first = ctx.derived.get(self.v_mix_key)
             if v_first is None:
                 raise RuntimeError("sink attention: a layer mixes values before any layer of its key has made them")
-        ops.qkv_pairs_post(qkv, q, k_pages, v_pages, v_first, self.inv_freq, ctx.positions, ctx.token_req, cache.block_table,
-                           cache.page_size, H, G, dk, dv, self.rot_dims, mode, self.mix)
+        # rotation factors and cache places are the same in every layer that shares them: made once per step
+        rot = slots = None
+        if self.rot_dims:
+            if self.rot_key not in ctx.derived:
+                ctx.derived[self.rot_key] = ops.rope_pairs_table(ctx.positions, self.inv_freq, self.rot_dims)
+            rot = ctx.derived[self.rot_key]
+        if k_pages is not None:
+            skey = ("slots", cache.block_table.data_ptr(), cache.page_size)
+            if skey not in ctx.derived:
+                ctx.derived[skey] = ops.slot_mapping(ctx.positions, ctx.token_req, cache.block_table, cache.page_size)
+            slots = ctx.derived[skey]
+        ops.qkv_pairs_post(qkv, q, k_pages, v_pages, v_first, rot, slots, cache.page_size, H, G, dk, dv, self.rot_dims, mode, self.mix)
         out = torch.empty((n, H * dv), dtype=self.rt.dtype, device=qkv.device)
         from ..kernels import attention as attn_kernels
         attn_kernels.paged_sink_attention(q, cache, out, ctx, H, G, dk, dv, self.window, self.scale, self.sink)

@@ -33,7 +33,7 @@ def bf16_round(a):
 
 
 # ---- mechanisms alone ---------------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("d,groups", [(64, 1), (60, 3), (256, 8), (512, 32), (4096, 2), (96, 96)])
+@pytest.mark.parametrize("d,groups", [(64, 1), (60, 3), (256, 8), (512, 32), (4096, 2), (96, 96), (2048, 4), (8192, 1), (768, 3)])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_group_norm_chain(d, groups, dtype):
     from mimirmind_b200.kernels import ops
@@ -219,11 +219,18 @@ def test_one_key_that_stands_out_is_seen_exactly_inside_the_window(window, page,
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_pair_rotation_value_mixing_and_cache_write(dtype):
+@pytest.mark.parametrize("H,G,dk,dv,rots", [(3, 2, 10, 6, ((10, 10000.0), (4, 500000.0), (0, 1.0))),
+                                            (4, 2, 32, 16, ((32, 10000.0), (8, 500000.0), (0, 1.0))),      # 16-byte chunks
+                                            (2, 1, 96, 32, ((64, 300.0), (12, 10000.0)))])
+def test_pair_rotation_value_mixing_and_cache_write_sizes(H, G, dk, dv, rots, dtype):
+    _pair_rotation_case(H, G, dk, dv, rots, dtype)
+
+
+def _pair_rotation_case(H, G, dk, dv, rots, dtype):
     from mimirmind_b200.kernels import ops
     rng = np.random.RandomState(9)
-    H, G, dk, dv, page, n = 3, 2, 10, 6, 8, 21
-    for rot_dims, base in ((10, 10000.0), (4, 500000.0), (0, 1.0)):
+    page, n = 8, 21
+    for rot_dims, base in rots:
         start = 1000
         positions = np.arange(start, start + n)
         qkv = bf16_round(rng.randn(n, (H + G) * dk + G * dv))
@@ -236,8 +243,10 @@ def test_pair_rotation_value_mixing_and_cache_write(dtype):
         vp = torch.zeros((n_pages, G, page, dv), dtype=DT[dtype], device=DEV)
         q_out = torch.empty((n, H * dk), dtype=DT[dtype], device=DEV)
         vf = dev(v_first, DT[dtype])
-        ops.qkv_pairs_post(dev(qkv, DT[dtype]), q_out, kp, vp, vf, dev(inv_freq), dev(positions, torch.int32), torch.zeros(n, dtype=torch.int32, device=DEV),
-                           table, page, H, G, dk, dv, rot_dims, 2, lam)
+        d_pos, d_req = dev(positions, torch.int32), torch.zeros(n, dtype=torch.int32, device=DEV)
+        rot = ops.rope_pairs_table(d_pos, dev(inv_freq), rot_dims) if rot_dims else None
+        slots = ops.slot_mapping(d_pos, d_req, table, page)
+        ops.qkv_pairs_post(dev(qkv, DT[dtype]), q_out, kp, vp, vf, rot, slots, page, H, G, dk, dv, rot_dims, 2, lam)
         q = qkv[:, :H * dk].reshape(n, H, dk)
         k = qkv[:, H * dk:(H + G) * dk].reshape(n, G, dk)
         v = qkv[:, (H + G) * dk:].reshape(n, G, dv)
@@ -252,8 +261,7 @@ def test_pair_rotation_value_mixing_and_cache_write(dtype):
         assert np.abs(got_k - want_k).max() < tol * 4 and np.abs(got_v - want_v).max() < tol
         # a source layer hands its values on unchanged
         out = torch.zeros((n, G * dv), dtype=DT[dtype], device=DEV)
-        ops.qkv_pairs_post(dev(qkv, DT[dtype]), q_out, kp, vp, out, dev(inv_freq), dev(positions, torch.int32), torch.zeros(n, dtype=torch.int32, device=DEV),
-                           table, page, H, G, dk, dv, rot_dims, 1, 0.0)
+        ops.qkv_pairs_post(dev(qkv, DT[dtype]), q_out, kp, vp, out, rot, slots, page, H, G, dk, dv, rot_dims, 1, 0.0)
         assert np.array_equal(out.float().cpu().numpy(), qkv[:, (H + G) * dk:].astype(np.float32))
 
 
@@ -267,13 +275,16 @@ def test_mingru_walk_and_chunked_scan(dtype):
     starts = np.cumsum([0] + lens)[:-1]
     n = sum(lens)
     a = rng.randn(n, 3 * W).astype(np.float32) * 2
+    bias = rng.randn(2 * W).astype(np.float32)
+    ab = a.astype(np.float64).copy()
+    ab[:, :2 * W] += bias                                                # what the recurrence sees
     slots = np.array([3, 0, 2, 1], dtype=np.int32)
     first_pos = [0, 5, 0, 77]                                            # two requests go on from a state, two start
     state0 = rng.randn(4, W).astype(np.float32)
     want_y, want_state = np.zeros((n, W)), state0.astype(np.float64).copy()
     for r, (s, ln) in enumerate(zip(starts, lens)):
         init = np.zeros(W) if first_pos[r] == 0 else state0[slots[r]].astype(np.float64)
-        z, u, g = pb.sigmoid(a[s:s + ln, :W].astype(np.float64)), a[s:s + ln, W:2 * W].astype(np.float64), a[s:s + ln, 2 * W:].astype(np.float64)
+        z, u, g = pb.sigmoid(ab[s:s + ln, :W]), ab[s:s + ln, W:2 * W], ab[s:s + ln, 2 * W:]
         S, last = pb.mingru_scan(z, u, init)
         want_y[s:s + ln] = S * (g * pb.sigmoid(g))
         want_state[slots[r]] = last
@@ -283,7 +294,7 @@ def test_mingru_walk_and_chunked_scan(dtype):
     # the walk
     state = dev(state0)
     y = torch.empty((n, W), dtype=DT[dtype], device=DEV)
-    ops.mingru_walk(dev(a), y, state, dev(meta, torch.int32), dev(slots, torch.int32), dev(positions, torch.int32), 4)
+    ops.mingru_walk(dev(a), y, state, dev(meta, torch.int32), dev(slots, torch.int32), dev(positions, torch.int32), 4, dev(bias))
     assert np.abs(y.float().cpu().numpy() - want_y).max() <= tol * np.abs(want_y).max()
     assert np.abs(state.cpu().numpy() - want_state).max() <= 3e-6 * np.abs(want_state).max()
     # the scan over chunks
@@ -295,7 +306,7 @@ def test_mingru_walk_and_chunked_scan(dtype):
     assert chunk_meta.shape[0] == sum(-(-ln // part.CHUNK) for ln in lens)
     state = dev(state0)
     y2 = torch.empty((n, W), dtype=DT[dtype], device=DEV)
-    ops.mingru_chunked(dev(a), y2, state, chunk_meta, req_chunks, dev(slots, torch.int32), dev(positions, torch.int32))
+    ops.mingru_chunked(dev(a), y2, state, chunk_meta, req_chunks, dev(slots, torch.int32), dev(positions, torch.int32), dev(bias))
     assert np.abs(y2.float().cpu().numpy() - want_y).max() <= tol * np.abs(want_y).max()
     assert np.abs(state.cpu().numpy() - want_state).max() <= 3e-6 * np.abs(want_state).max()
     # one token per request without a request table (a decode batch): request r is token r
