@@ -9,9 +9,11 @@
 //   * prefill: one CTA per (tile of 64 query tokens of one request, query head); keys and values stream through
 //     shared memory in tiles of 64 keys gathered page by page with cp.async, two stages deep; online softmax.  Only
 //     the key tiles between the first row's window edge and the last row's position are visited.
-//   * decode: one CTA per (token, KV head).  The rows of the tile are the query heads that share the KV head, so a
-//     key or value is read once for all of them; the four warps take 16 keys each of every 64-key tile and are merged
-//     through shared memory.  Positions come from the device, so a captured step replays with new positions.
+//   * decode: one CTA per (token, KV head, split of the token's key tiles).  The rows of the tile are the query heads
+//     that share the KV head, so a key or value is read once for all of them; the four warps take 16 keys each of every
+//     64-key tile and are merged through shared memory; with more than one split the partial results go through scratch
+//     memory and a merge launch, which also adds the sink.  Positions come from the device, so a captured step replays
+//     with new positions.
 //
 // Same tiling as csrc/attention_mma.cu (equal key and value sizes, no sink), which this file generalises.
 #include "common.cuh"
@@ -229,7 +231,8 @@ __global__ void __launch_bounds__(SATT_THREADS) attention_sink_prefill_kernel(
 template <int DK, int DV>
 __global__ void __launch_bounds__(SATT_THREADS) attention_sink_decode_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
-    const __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ out, const int32_t* __restrict__ items,
+    const __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
+    float* __restrict__ part_ml, const int32_t* __restrict__ items,
     const int32_t* __restrict__ positions, const int32_t* __restrict__ token_req, const int32_t* __restrict__ block_table,
     int table_width, int page_size, int H, int G, int window, float scale_log2, int sink) {
     constexpr int KS = DK + 8, VS = DV + 8;
@@ -244,7 +247,11 @@ __global__ void __launch_bounds__(SATT_THREADS) attention_sink_decode_kernel(
     const int pos = positions[t];
     const int k_end = pos + 1;
     const int k_begin = (window > 0 && k_end > window) ? k_end - window : 0;
-    const int kt_begin = k_begin / SKT, kt_end = (k_end + SKT - 1) / SKT;
+    // gridDim.z CTAs share the token's key tiles evenly (a CTA may get none: it posts an empty partial result)
+    const int n_splits = gridDim.z, split = blockIdx.z;
+    const int kt_first = k_begin / SKT, kt_last = (k_end + SKT - 1) / SKT;
+    const int per_split = (kt_last - kt_first + n_splits - 1) / n_splits;
+    const int kt_begin = min(kt_last, kt_first + split * per_split), kt_end = min(kt_last, kt_begin + per_split);
     const int32_t* table = block_table + (size_t)token_req[t] * table_width;
     const int qpg = H / G;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -378,20 +385,51 @@ __global__ void __launch_bounds__(SATT_THREADS) attention_sink_decode_kernel(
         }
     }
     __syncthreads();
+    const bool single = n_splits == 1;
     for (int idx = threadIdx.x; idx < qpg * DV; idx += SATT_THREADS) {
         const int r = idx / DV, col = idx - r * DV;
-        float m = sink ? 0.0f : -INFINITY;
+        float m = (sink && single) ? 0.0f : -INFINITY;
 #pragma unroll
         for (int w = 0; w < 4; ++w) m = fmaxf(m, mml[(w * 16 + r) * 2]);
         const float mu = (m == -INFINITY) ? 0.0f : m;
-        float l = sink ? exp2f(-mu) : 0.0f, acc = 0.0f;
+        float l = (sink && single) ? exp2f(-mu) : 0.0f, acc = 0.0f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
             const float f = exp2f(mml[(w * 16 + r) * 2] - mu);
             l += mml[(w * 16 + r) * 2 + 1] * f;
             acc += mo[((size_t)w * 16 + r) * DV + col] * f;
         }
-        out[((size_t)t * H + g * qpg + r) * DV + col] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+        const int h = g * qpg + r;
+        if (single) {
+            out[((size_t)t * H + h) * DV + col] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+        } else {
+            const size_t p = ((size_t)item * H + h) * n_splits + split;
+            part_o[p * DV + col] = acc;
+            if (col == 0) {
+                part_ml[p * 2] = m;
+                part_ml[p * 2 + 1] = l;
+            }
+        }
+    }
+}
+
+// The splits of every (item, head) put together in split order, with the sink's share: one block per (item, head).
+__global__ void attention_sink_merge_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o,
+                                            const float* __restrict__ part_ml, const int32_t* __restrict__ items, int H, int dv,
+                                            int n_splits, int sink) {
+    const int item = blockIdx.x, h = blockIdx.y;
+    const int t = items ? items[item] : item;
+    const size_t p0 = ((size_t)item * H + h) * n_splits;
+    float m = sink ? 0.0f : -INFINITY;
+    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_ml[(p0 + s) * 2]);
+    const float mu = (m == -INFINITY) ? 0.0f : m;
+    float l = sink ? exp2f(-mu) : 0.0f;
+    for (int s = 0; s < n_splits; ++s) l += part_ml[(p0 + s) * 2 + 1] * exp2f(part_ml[(p0 + s) * 2] - mu);
+    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+    for (int col = threadIdx.x; col < dv; col += blockDim.x) {
+        float acc = 0.0f;
+        for (int s = 0; s < n_splits; ++s) acc += part_o[(p0 + s) * dv + col] * exp2f(part_ml[(p0 + s) * 2] - mu);
+        out[((size_t)t * H + h) * dv + col] = __float2bfloat16_rn(acc * inv);
     }
 }
 
@@ -416,7 +454,8 @@ static int launch_sink_prefill(const void* q, const void* k, const void* v, void
 }
 
 template <int DK, int DV>
-static int launch_sink_decode(const void* q, const void* k, const void* v, void* out, const void* items, int n_items,
+static int launch_sink_decode(const void* q, const void* k, const void* v, void* out, void* part_o, void* part_ml, int n_splits,
+                              const void* items, int n_items,
                               const void* positions, const void* token_req, const void* table, int table_width, int page_size,
                               int H, int G, int window, float scale, int sink, cudaStream_t s) {
     const size_t kv = (size_t)SDEC_STAGES * 64 * (DK + 8 + DV + 8) * sizeof(__nv_bfloat16);
@@ -428,10 +467,16 @@ static int launch_sink_decode(const void* q, const void* k, const void* v, void*
         mm_set_last_error("sink attention: shared memory for the decode tiles could not be set");
         return MM_ERR_UNSUPPORTED;
     }
-    mm_launch(kernel, dim3(n_items, G), dim3(SATT_THREADS), smem, s, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k,
-              (const __nv_bfloat16*)v, (__nv_bfloat16*)out, (const int32_t*)items, (const int32_t*)positions, (const int32_t*)token_req,
-              (const int32_t*)table, table_width, page_size, H, G, window, scale * SINK_LOG2E, sink);
+    mm_launch(kernel, dim3(n_items, G, n_splits), dim3(SATT_THREADS), smem, s, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k,
+              (const __nv_bfloat16*)v, (__nv_bfloat16*)out, (float*)part_o, (float*)part_ml, (const int32_t*)items,
+              (const int32_t*)positions, (const int32_t*)token_req, (const int32_t*)table, table_width, page_size, H, G, window,
+              scale * SINK_LOG2E, sink);
     MM_CHECK_LAUNCH();
+    if (n_splits > 1) {
+        mm_launch(attention_sink_merge_kernel, dim3(n_items, H), dim3(DV >= 64 ? 64 : 32), 0, s, (__nv_bfloat16*)out, (const float*)part_o,
+                  (const float*)part_ml, (const int32_t*)items, H, DV, n_splits, sink);
+        MM_CHECK_LAUNCH();
+    }
     return MM_OK;
 }
 
@@ -474,16 +519,21 @@ MM_EXPORT int mm_attention_sink_prefill_bf16(const void* q, const void* k_pages,
     return MM_ERR_UNSUPPORTED;
 }
 
-MM_EXPORT int mm_attention_sink_decode_bf16(const void* q, const void* k_pages, const void* v_pages, void* out, const void* items,
+// n_splits > 1: the key tiles of every token are shared out over that many CTAs, whose partial results go through
+// part_o [n_items, H, n_splits, dv] and part_ml [n_items, H, n_splits, 2] (fp32) and a merge launch.
+MM_EXPORT int mm_attention_sink_decode_bf16(const void* q, const void* k_pages, const void* v_pages, void* out, void* part_o,
+                                            void* part_ml, int n_splits, const void* items,
                                             int n_items, const void* positions, const void* token_req, const void* block_table,
                                             int table_width, int page_size, int H, int G, int dk, int dv, int window, float scale,
                                             int sink, void* stream) {
+    MM_REQUIRE(n_splits >= 1 && n_splits <= 64 && (n_splits == 1 || (part_o != nullptr && part_ml != nullptr)),
+               "sink attention: 1..64 splits, with scratch for more than one");
     MM_REQUIRE(n_items >= 0 && H > 0 && G > 0 && H % G == 0 && H / G <= 16, "sink attention: at most 16 query heads per kv head");
     MM_REQUIRE(page_size > 0 && table_width > 0 && window >= 0, "sink attention: bad page geometry or window");
     if (n_items == 0) return MM_OK;
     cudaStream_t s = (cudaStream_t)stream;
-    SINK_DISPATCH(launch_sink_decode, q, k_pages, v_pages, out, items, n_items, positions, token_req, block_table, table_width, page_size,
-                  H, G, window, scale, sink, s);
+    SINK_DISPATCH(launch_sink_decode, q, k_pages, v_pages, out, part_o, part_ml, n_splits, items, n_items, positions, token_req, block_table,
+                  table_width, page_size, H, G, window, scale, sink, s);
     mm_set_last_error("sink attention: key and value sizes must each be one of 32, 64, 96, 128");
     return MM_ERR_UNSUPPORTED;
 }

@@ -113,7 +113,7 @@ __global__ void __launch_bounds__(ATT_TC_THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                             const __grid_constant__ CUtensorMap tmV, __nv_bfloat16* __restrict__ out,
                             const int32_t* __restrict__ tiles, const int32_t* __restrict__ block_table, int table_width,
-                            int page_size, int H, int G, int window, float scale_log2, int* __restrict__ err) {
+                            int page_size, int H, int G, int window, float scale_log2, int sink, int* __restrict__ err) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];   // 128-byte swizzle wants 1024-byte aligned tiles
     if ((smem_u32(smem_raw) & 1023u) != 0) {                      // never seen; without the alignment nothing below is valid
         if (threadIdx.x == 0 && err != nullptr) atomicExch(err, 3);
@@ -378,7 +378,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
         const float m = fmaxf(m0, m1);
         const float f0 = (m0 == -INFINITY) ? 0.0f : fast_exp2((m0 - m) * scale_log2);
         const float f1 = (m1 == -INFINITY) ? 0.0f : fast_exp2((m1 - m) * scale_log2);
-        const float total = l0 * f0 + l1 * f1;
+        // a softmax sink (a key of score 0 without a value) only adds its weight, 2^(-m scale), to the row's sum
+        const float total = l0 * f0 + l1 * f1 + (sink ? fast_exp2(-m * scale_log2) : 0.0f);
         // O of both groups is complete when their last P V is done (a group without tiles has no O)
         const int tiles0 = (n_tiles_k + 1) / 2, tiles1 = n_tiles_k / 2;
         if (ok && tiles0 > 0) ok = mbar_wait(smem_u32(&ctl->pv_done[0]), (uint32_t)(tiles0 - 1) & 1, abort_flag);
@@ -430,10 +431,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
 // q, out: [n_tokens, H*hd] bf16; k_pages, v_pages: [num_pages, G, page_size, hd] bf16 of one layer (hd 64 or 128);
 // tiles: int32 [n_tiles, 4] (request, first row, rows <= 128, first position).  `err`: device int set to 2 when a
 // bounded wait ran out (may be null).
-MM_EXPORT int mm_attention_prefill_tcgen05(const void* q, const void* k_pages, const void* v_pages, void* out,
-                                           const void* tiles, int n_tiles, const void* block_table, int table_width,
-                                           int page_size, int num_pages, int n_tokens, int H, int G, int hd, int window,
-                                           float scale, void* err, void* stream) {
+static int attention_prefill_tcgen05_launch(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                            const void* tiles, int n_tiles, const void* block_table, int table_width,
+                                            int page_size, int num_pages, int n_tokens, int H, int G, int hd, int window,
+                                            float scale, int sink, void* err, void* stream) {
     MM_REQUIRE(hd == 128 || hd == 64, "attention_prefill_tcgen05: built for head sizes 64 and 128");
     MM_REQUIRE(n_tiles >= 0 && H > 0 && G > 0 && H % G == 0 && n_tokens > 0 && num_pages > 0, "attention_prefill_tcgen05: bad sizes");
     MM_REQUIRE(page_size >= 8 && page_size <= 128 && (128 % page_size) == 0, "attention_prefill_tcgen05: page_size must be 8, 16, 32, 64 or 128");
@@ -465,11 +466,29 @@ MM_EXPORT int mm_attention_prefill_tcgen05(const void* q, const void* k_pages, c
     if (hd == 128)
         attention_prefill_tc_kernel<128><<<grid, ATT_TC_THREADS, smem, (cudaStream_t)stream>>>(
             tq, tk, tv, (__nv_bfloat16*)out, (const int32_t*)tiles, (const int32_t*)block_table, table_width, page_size, H, G,
-            window, scale * LOG2E, (int*)err);
+            window, scale * LOG2E, sink, (int*)err);
     else
         attention_prefill_tc_kernel<64><<<grid, ATT_TC_THREADS, smem, (cudaStream_t)stream>>>(
             tq, tk, tv, (__nv_bfloat16*)out, (const int32_t*)tiles, (const int32_t*)block_table, table_width, page_size, H, G,
-            window, scale * LOG2E, (int*)err);
+            window, scale * LOG2E, sink, (int*)err);
     MM_CHECK_LAUNCH();
     return MM_OK;
+}
+
+MM_EXPORT int mm_attention_prefill_tcgen05(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                           const void* tiles, int n_tiles, const void* block_table, int table_width,
+                                           int page_size, int num_pages, int n_tokens, int H, int G, int hd, int window,
+                                           float scale, void* err, void* stream) {
+    return attention_prefill_tcgen05_launch(q, k_pages, v_pages, out, tiles, n_tiles, block_table, table_width, page_size, num_pages,
+                                            n_tokens, H, G, hd, window, scale, 0, err, stream);
+}
+
+// The same with a softmax sink: one is added to every row's denominator (scale must be positive).
+MM_EXPORT int mm_attention_prefill_tcgen05_sink(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                                const void* tiles, int n_tiles, const void* block_table, int table_width,
+                                                int page_size, int num_pages, int n_tokens, int H, int G, int hd, int window,
+                                                float scale, int sink, void* err, void* stream) {
+    MM_REQUIRE(scale > 0.0f, "attention_prefill_tcgen05: the scale must be positive");
+    return attention_prefill_tcgen05_launch(q, k_pages, v_pages, out, tiles, n_tiles, block_table, table_width, page_size, num_pages,
+                                            n_tokens, H, G, hd, window, scale, sink, err, stream);
 }

@@ -23,6 +23,7 @@ def paged_attention(q, cache, out, ctx, num_heads: int, num_kv_heads: int, head_
                                  cache.block_table, cache.page_size, num_heads, num_kv_heads, head_dim, window, scale)
 
 
+USE_SINK_TCGEN05 = True    # False: portions never take the tcgen05 prefill kernel (tests compare it with the mma.sync one)
 USE_SINK_MMA = True        # False: the sink attention always runs the fp32-arithmetic kernel (tests compare the two)
 SINK_PREFILL_MIN = 16      # shorter portions go token by token through the decode kernel
 SINK_TILE_ROWS = 64
@@ -37,24 +38,38 @@ def _sink_lib():
         P, I, F = c_void_p, c_int, c_float
         _lib.declare("mm_attention_sink_supported", [I, I])
         _lib.declare("mm_attention_sink_prefill_bf16", [P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, P])
-        _lib.declare("mm_attention_sink_decode_bf16", [P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P])
+        _lib.declare("mm_attention_sink_decode_bf16", [P, P, P, P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P])
+        _lib.declare("mm_attention_prefill_tcgen05_sink", [P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, F, I, P, P])
         _sink_declared = True
     return _lib.load()
 
 
-def sink_plan(ctx, n_tokens: int):
-    """The step's tokens sorted once, on the host, into prefill tiles (64 query tokens of one request; portions of at
-    least SINK_PREFILL_MIN tokens) and decode items (single tokens); every layer of the step reuses it.  Returns
+SINK_TARGET_CTAS = 2 * 148     # decode CTAs wanted: the key tiles of a token are shared out until the GPU is full
+SINK_MAX_SPLITS = 16
+
+
+def sink_splits(n_items: int, num_kv_heads: int, window: int, max_kv_len: int) -> int:
+    """CTAs per (token, KV head) of the decode kernel: enough to fill the GPU, never more than the token has key tiles."""
+    ctas = max(1, n_items * num_kv_heads)
+    if ctas >= SINK_TARGET_CTAS // 2:
+        return 1
+    keys = min(window, max_kv_len) if window > 0 else max_kv_len
+    return max(1, min(-(-SINK_TARGET_CTAS // ctas), -(-keys // 64), SINK_MAX_SPLITS))
+
+
+def sink_plan(ctx, n_tokens: int, tile_rows: int = SINK_TILE_ROWS):
+    """The step's tokens sorted once, on the host, into prefill tiles (``tile_rows`` query tokens of one request; portions
+    of at least SINK_PREFILL_MIN tokens) and decode items (single tokens); every layer of the step reuses it.  Returns
     (tiles [n, 4] or None, n_tiles, items [m] or None, n_items); items None with n_items > 0 means every token."""
-    key = ("sink_attention_plan",)
+    key = ("sink_attention_plan", tile_rows)
     plan = ctx.plans.get(key)
     if plan is None:
         tiles, items = [], []
         for r in range(ctx.n_requests):
             s, n, kv = ctx.q_start[r], ctx.q_len[r], ctx.kv_len[r]
             if n >= SINK_PREFILL_MIN:
-                for off in range(0, n, SINK_TILE_ROWS):
-                    tiles.append((r, s + off, min(SINK_TILE_ROWS, n - off), kv - n + off))
+                for off in range(0, n, tile_rows):
+                    tiles.append((r, s + off, min(tile_rows, n - off), kv - n + off))
             else:
                 items.extend(range(s, s + n))
         tiles.sort(key=lambda tile: tile[3] + tile[2])
@@ -76,15 +91,34 @@ def paged_sink_attention(q, cache, out, ctx, num_heads: int, num_kv_heads: int, 
             and _sink_lib().mm_attention_sink_supported(key_dim, value_dim)):
         from .lib import check
         lib = _sink_lib()
-        tiles, n_tiles, items, n_items = sink_plan(ctx, q.shape[0])
+        # equal key and value sizes of 64 or 128: the tcgen05 prefill kernel of the plain attention, told of the sink
+        from . import attention_bf16
+        tensor_memory = (USE_SINK_TCGEN05 and key_dim == value_dim and attention_bf16.tcgen05_prefill_usable(key_dim, cache.page_size))
+        tiles, n_tiles, items, n_items = sink_plan(ctx, q.shape[0], attention_bf16.TILE_ROWS_TC if tensor_memory else SINK_TILE_ROWS)
         stream = ops._stream()
-        if n_tiles:
+        if n_tiles and tensor_memory:
+            check(lib.mm_attention_prefill_tcgen05_sink(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), tiles.data_ptr(),
+                                                        n_tiles, table.data_ptr(), table.shape[1], cache.page_size, k_pages.shape[0],
+                                                        q.shape[0], num_heads, num_kv_heads, key_dim, int(window), float(scale),
+                                                        int(bool(sink)), ops.tcgen05_error_flag(q.device).data_ptr(), stream),
+                  "attention_prefill_tcgen05_sink")
+        elif n_tiles:
             check(lib.mm_attention_sink_prefill_bf16(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), tiles.data_ptr(),
                                                      n_tiles, table.data_ptr(), table.shape[1], cache.page_size, num_heads, num_kv_heads,
                                                      key_dim, value_dim, int(window), float(scale), int(bool(sink)), stream),
                   "attention_sink_prefill_bf16")
         if n_items:
+            splits = sink_splits(n_items, num_kv_heads, window, ctx.max_kv_len)
+            part_o = part_ml = None
+            if splits > 1:
+                skey = ("sink_attention_scratch", n_items, num_heads, splits, value_dim)
+                if skey not in ctx.plans:
+                    ctx.plans[skey] = (torch.empty((n_items, num_heads, splits, value_dim), dtype=torch.float32, device=q.device),
+                                       torch.empty((n_items, num_heads, splits, 2), dtype=torch.float32, device=q.device))
+                part_o, part_ml = ctx.plans[skey]
             check(lib.mm_attention_sink_decode_bf16(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(),
+                                                    part_o.data_ptr() if part_o is not None else None,
+                                                    part_ml.data_ptr() if part_ml is not None else None, splits,
                                                     items.data_ptr() if items is not None else None, n_items, ctx.positions.data_ptr(),
                                                     ctx.token_req.data_ptr(), table.data_ptr(), table.shape[1], cache.page_size, num_heads,
                                                     num_kv_heads, key_dim, value_dim, int(window), float(scale), int(bool(sink)), stream),

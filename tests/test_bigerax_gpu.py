@@ -124,12 +124,15 @@ def _paged(k, v, page_size, rng, dtype):
 @pytest.mark.parametrize("H,G,dk,dv,window,page", [(4, 2, 24, 16, 19, 16), (3, 3, 9, 7, 40, 8), (8, 1, 64, 64, 0, 16), (4, 4, 96, 32, 33, 32),
                                                    (2, 1, 128, 128, 130, 16), (2, 2, 16, 200, 5, 16), (16, 1, 32, 96, 100, 16),
                                                    (6, 2, 128, 64, 0, 64)])
-@pytest.mark.parametrize("tensor_cores", [True, False])
-def test_sink_attention_against_the_plain_one(H, G, dk, dv, window, page, dtype, tensor_cores, monkeypatch):
+@pytest.mark.parametrize("kernels", ["tcgen05", "mma", "plain"])
+def test_sink_attention_against_the_plain_one(H, G, dk, dv, window, page, dtype, kernels, monkeypatch):
     from mimirmind_b200.kernels import attention
-    if dtype == "float32" and not tensor_cores:
+    if dtype == "float32" and kernels != "plain":
         pytest.skip("the 32-bit path has one kernel")
-    monkeypatch.setattr(attention, "USE_SINK_MMA", tensor_cores)
+    if kernels == "tcgen05" and not (dk == dv and dk in (64, 128)):
+        pytest.skip("the tcgen05 prefill kernel takes equal key and value sizes of 64 or 128")
+    monkeypatch.setattr(attention, "USE_SINK_MMA", kernels != "plain")
+    monkeypatch.setattr(attention, "USE_SINK_TCGEN05", kernels == "tcgen05")
     from mimirmind_b200.parts.base import LayerCache
     rng = np.random.RandomState(H * 100 + dk)
     T, scale = 300, 0.37 / np.sqrt(dk) * 4
@@ -174,15 +177,15 @@ def test_sink_attention_against_the_plain_one(H, G, dk, dv, window, page, dtype,
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("window,page", [(40, 16), (64, 16), (17, 8), (0, 16), (65, 32)])
-@pytest.mark.parametrize("dv", [8, 32])
-def test_one_key_that_stands_out_is_seen_exactly_inside_the_window(window, page, dtype, dv):
+@pytest.mark.parametrize("dk,dv", [(32, 8), (32, 32), (64, 64)])
+def test_one_key_that_stands_out_is_seen_exactly_inside_the_window(window, page, dtype, dk, dv):
     """Every key is orthogonal to the query but one, whose score stands out by far and whose value is a marker: the
     output shows the marker exactly when that key is inside the window, in a prompt and for a single decoded token, with
     the key at a page's border, far back, and just inside and just outside the window."""
     from mimirmind_b200.kernels import attention
     from mimirmind_b200.parts.base import LayerCache
-    H, G = 4, 2                     # values of 8 run the fp32-arithmetic kernel, of 32 the tensor-core kernels (bfloat16)
-    dk, T = 32, 400
+    H, G = 4, 2                     # bfloat16: values of 8 run the fp32-arithmetic kernel, 32 the mma.sync kernels, 64/64 tcgen05
+    T = 400
     rng = np.random.RandomState(window + page)
 
     class Ctx:
