@@ -38,6 +38,16 @@
 #define GEMV_THREADS 256
 #define GEMV_WARPS 8
 
+// the activations a plain product may apply after its bias (fp32)
+__device__ __forceinline__ float gemv_activation(float z, int act) {
+    switch (act) {
+        case 1: { const float r = fmaxf(z, 0.0f); return r * r; }
+        case 2: return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+        case 3: return z / (1.0f + expf(-z));
+        default: return fmaxf(z, 0.0f);
+    }
+}
+
 struct GemvArgs {
     const __nv_bfloat16* W;
     const __nv_bfloat16* x;
@@ -45,6 +55,7 @@ struct GemvArgs {
     void* out;
     int M, N, K, ldx, ldo;
     int bias_dtype, out_dtype;
+    int act;                    // PLAIN: activation after the bias (0 none, 1 squared relu, 2 gelu (tanh form), 3 silu, 4 relu)
     int RT, KS;
     // deferred 1/rms of the input rows (null: none): partial sums of squares [in_tiles][16]
     const float* in_ss;
@@ -392,6 +403,7 @@ __device__ __forceinline__ void gemv_item(const GemvArgs& a, int item, const Gem
                     const int row = n0 + r + hi * 8;
                     float v = acc[j][hi * 2 + e];
                     if (a.bias) v += (a.bias_dtype == MM_F32) ? ((const float*)a.bias)[row] : __bfloat162float(((const __nv_bfloat16*)a.bias)[row]);
+                    if (a.act) v = gemv_activation(v, a.act);
                     const size_t o = (size_t)m * a.ldo + row;
                     if (a.out_dtype == MM_F32) ((float*)a.out)[o] = v; else ((__nv_bfloat16*)a.out)[o] = __float2bfloat16_rn(v);
                 }
@@ -502,6 +514,19 @@ MM_EXPORT int mm_gemv_bf16(const void* W, const void* x, const void* bias, int b
     a.bias = bias; a.bias_dtype = bias_dtype; a.out = out; a.out_dtype = out_dtype; a.ldo = ldo;
     cudaStream_t s = (cudaStream_t)stream;
     return swiglu ? launch_gemv<EPI_SWIGLU>(a, s) : launch_gemv<EPI_PLAIN>(a, s);
+}
+
+// out[M, ldo] = act(x * W^T + bias): the plain product with an activation after the bias (act: 1 squared relu, 2 gelu in its
+// tanh form, 3 silu, 4 relu), so that a feed-forward's hidden rows of a few tokens are made in one launch.
+MM_EXPORT int mm_gemv_bf16_act(const void* W, const void* x, const void* bias, int bias_dtype, void* out, int out_dtype,
+                               int M, int N, int K, int ldx, int ldo, int rt, int ks, int act, void* stream) {
+    GemvArgs a;
+    const int rc = gemv_common(a, W, x, M, N, K, ldx, rt, ks, nullptr, 0, 0, 0.0f);
+    if (rc != MM_OK) return rc;
+    MM_REQUIRE(out_dtype == MM_F32 || out_dtype == MM_BF16, "gemv: out dtype must be float32 or bfloat16");
+    MM_REQUIRE(ldo >= N && act >= 1 && act <= 4, "gemv: ldo too small or unknown activation");
+    a.bias = bias; a.bias_dtype = bias_dtype; a.out = out; a.out_dtype = out_dtype; a.ldo = ldo; a.act = act;
+    return launch_gemv<EPI_PLAIN>(a, (cudaStream_t)stream);
 }
 
 // residual[M, N] (fp32) += x * W^T.  With norm_w: also xw_out[M, N] = bf16(residual * norm_w) and

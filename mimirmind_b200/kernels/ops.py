@@ -804,6 +804,23 @@ def mingru_chunked(a: torch.Tensor, y: torch.Tensor, state: torch.Tensor, chunk_
 ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}
 
 
+def gemv_bf16_act(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], activation: str) -> torch.Tensor:
+    """act(x[M<=8, K] @ w[N, K]^T + bias) in one launch of the weight-streaming kernel (the activation on the fp32 sums)."""
+    _need(x, "gemv x", torch.bfloat16)
+    _need(w, "gemv w", torch.bfloat16)
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape != (n, k) or not gemv_supported(m, n, k):
+        raise KernelError(f"gemv: shapes x{tuple(x.shape)} w{tuple(w.shape)} are not supported")
+    if bias is not None:
+        _need(bias, "gemv bias")
+    out = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+    rt, ks = _gemv_layout(n, k)
+    check(_lib.load().mm_gemv_bf16_act(w.data_ptr(), x.data_ptr(), _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32,
+                                       out.data_ptr(), BF16, m, n, k, k, n, rt, ks, ACTIVATIONS[activation] + 1, _stream()), "gemv_bf16_act")
+    return out
+
+
 def bias_act(x: torch.Tensor, bias: Optional[torch.Tensor], activation: str, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out = act(x + bias) in fp32 arithmetic; ``activation`` one of relu2 (squared relu), gelu_tanh, silu, relu."""
     _need(x, "bias_act x")

@@ -117,6 +117,11 @@ class DenseMLP(FeedForward):
             self.b_down = weights.take(spec["down"] + sfx).contiguous()
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        if (x.dtype == torch.bfloat16 and self.w_up.dtype == torch.bfloat16 and self.rt.matmul != "simt" and not ctx.plain_only
+                and ops.gemv_supported(x.shape[0], self.ff, self.hidden)):
+            # a few tokens: bias and activation in the epilogue of the weight-streaming product
+            hidden = ops.gemv_bf16_act(x, self.w_up, self.b_up, self.activation)
+            return linear(hidden, self.w_down, self.b_down, self.rt)
         hidden = linear(x, self.w_up, None, self.rt)
         ops.bias_act(hidden, self.b_up, self.activation, hidden)
         return linear(hidden, self.w_down, self.b_down, self.rt)

@@ -473,3 +473,39 @@ def test_the_replay_program_on_this_design(models, tmp_path):
     t.step([("last", [1, 2, 3], [])], end=["last"])
     out = ru.run_program(folder, "bfloat16", t, t.max_live_tokens(), str(tmp_path / "out"), cfg["vocab"])
     check_rows(t, out, reqs, ref, "bfloat16", "program")
+
+
+def test_the_command_line_generates_with_this_design(models, tmp_path):
+    """bin/mimirmind: random-weights mode writes a Bigerax folder from its config.json, smoke generates from it and from
+    a test model; the greedy tokens of the test model are the plain implementation's."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from conftest import ROOT
+    folder, cfg, w = models("S")
+    exe = [sys.executable, os.path.join(ROOT, "bin", "mimirmind")]
+    conf = {"defaultModel": "m", "models": [{"id": "m", "path": folder}], "runtime": {"dtype": "float32", "maxContextTokens": 256, "cacheTokens": 512}}
+    (tmp_path / "config.json").write_text(json.dumps(conf))
+    out = subprocess.run(exe + ["smoke", "--config", str(tmp_path / "config.json"), "--prompt", "5 17 3 150", "--max-new", "6"],
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    lines = out.stdout.strip().splitlines()
+    got = [int(t) for t in lines[0].split()]
+    assert len(got) == 6 and lines[1] == "generated 6"
+    toks = [5, 17, 3, 150]
+    for tok in got:
+        row = pb.forward(cfg, w, toks)[-1]
+        assert row[tok] >= row.max() - 1e-4
+        toks.append(tok)
+    (tmp_path / "mc.json").write_text(json.dumps(bu.CONFIGS["R"]))
+    rw = subprocess.run(exe + ["random-weights", "--model-config", str(tmp_path / "mc.json"), "--seed", "9", "--out", str(tmp_path / "rw"),
+                               "--dtype", "bfloat16"], capture_output=True, text=True, timeout=300)
+    assert rw.returncode == 0, rw.stderr
+    conf["models"][0]["path"] = str(tmp_path / "rw")
+    conf["runtime"]["dtype"] = "bfloat16"
+    (tmp_path / "config2.json").write_text(json.dumps(conf))
+    out = subprocess.run(exe + ["smoke", "--config", str(tmp_path / "config2.json"), "--prompt", "1 2 3", "--max-new", "4"],
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    assert out.stdout.strip().splitlines()[1] == "generated 4"
