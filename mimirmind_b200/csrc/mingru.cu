@@ -17,18 +17,25 @@
 
 #define MG_AHEAD 8
 
-__device__ __forceinline__ float sigmoid_f32(float x) { return 1.0f / (1.0f + expf(-x)); }
+// FAST: the hardware's exponential and reciprocal (about 2 units in the last place of fp32) for bfloat16 runs, whose
+// outputs are rounded to 8 bits anyway: with the exact functions the scan is bound by instructions (two exponentials
+// and two IEEE divisions per token and channel), not by memory.  float32 runs take the exact ones.
+template <bool FAST>
+__device__ __forceinline__ float sigmoid_f32(float x) {
+    return FAST ? __fdividef(1.0f, 1.0f + __expf(-x)) : 1.0f / (1.0f + expf(-x));
+}
 
+template <bool FAST>
 __device__ __forceinline__ void mingru_gate(float az, float ax, float& keep, float& add) {
-    const float z = sigmoid_f32(az);
-    const float c = ax >= 0.0f ? ax + 0.5f : sigmoid_f32(ax);
+    const float z = sigmoid_f32<FAST>(az);
+    const float c = ax >= 0.0f ? ax + 0.5f : sigmoid_f32<FAST>(ax);
     keep = 1.0f - z;
     add = z * c;
 }
 
 // n tokens from t0 on for channel c, starting from the state S; WRITE: y gets state * silu(gate); prod (if given)
 // gets the product of the keep factors.  Returns the last state.
-template <typename T, bool WRITE>
+template <typename T, bool WRITE, bool FAST>
 __device__ __forceinline__ float mingru_run(const float* __restrict__ a, T* __restrict__ y, int t0, int n, int c, int W, float bz,
                                             float bx, float S, float* prod) {
     float p = 1.0f;
@@ -46,10 +53,10 @@ __device__ __forceinline__ float mingru_run(const float* __restrict__ a, T* __re
         for (int k = 0; k < MG_AHEAD; ++k) {
             if (t + k < t0 + n) {
                 float keep, add;
-                mingru_gate(az[k] + bz, ax[k] + bx, keep, add);
+                mingru_gate<FAST>(az[k] + bz, ax[k] + bx, keep, add);
                 S = fmaf(keep, S, add);
                 p *= keep;
-                if (WRITE) y[(size_t)(t + k) * W + c] = from_f32<T>(S * (ag[k] * sigmoid_f32(ag[k])));
+                if (WRITE) y[(size_t)(t + k) * W + c] = from_f32<T>(S * (ag[k] * sigmoid_f32<FAST>(ag[k])));
             }
         }
     }
@@ -70,11 +77,12 @@ __global__ void mingru_walk_kernel(const float* __restrict__ a, T* __restrict__ 
     float* st = state + (size_t)slots[r] * W + c;
     float S = positions[t0] == 0 ? 0.0f : *st;
     const float bz = bias ? bias[c] : 0.0f, bx = bias ? bias[W + c] : 0.0f;
-    S = mingru_run<T, true>(a, y, t0, n, c, W, bz, bx, S, nullptr);
+    S = mingru_run<T, true, sizeof(T) == 2>(a, y, t0, n, c, W, bz, bx, S, nullptr);
     *st = S;
 }
 
 // pass 1: chunk k of request r (tokens t0 + k*chunk ...) from a zero state -> A[ck], B[ck]
+template <bool FAST>
 __global__ void mingru_chunk_reduce_kernel(const float* __restrict__ a, float* __restrict__ A, float* __restrict__ B,
                                            const int32_t* __restrict__ chunk_meta, const float* __restrict__ bias, int W) {
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -83,7 +91,7 @@ __global__ void mingru_chunk_reduce_kernel(const float* __restrict__ a, float* _
     const int t0 = chunk_meta[4 * ck], n = chunk_meta[4 * ck + 1];
     const float bz = bias ? bias[c] : 0.0f, bx = bias ? bias[W + c] : 0.0f;
     float prod;
-    const float S = mingru_run<float, false>(a, nullptr, t0, n, c, W, bz, bx, 0.0f, &prod);
+    const float S = mingru_run<float, false, FAST>(a, nullptr, t0, n, c, W, bz, bx, 0.0f, &prod);
     A[(size_t)ck * W + c] = prod;
     B[(size_t)ck * W + c] = S;
 }
@@ -119,7 +127,7 @@ __global__ void mingru_chunk_apply_kernel(const float* __restrict__ a, const flo
     if (c >= W) return;
     const int t0 = chunk_meta[4 * ck], n = chunk_meta[4 * ck + 1];
     const float bz = bias ? bias[c] : 0.0f, bx = bias ? bias[W + c] : 0.0f;
-    mingru_run<T, true>(a, y, t0, n, c, W, bz, bx, start[(size_t)ck * W + c], nullptr);
+    mingru_run<T, true, sizeof(T) == 2>(a, y, t0, n, c, W, bz, bx, start[(size_t)ck * W + c], nullptr);
 }
 
 MM_EXPORT int mm_mingru_walk(const void* a, void* y, int dtype, void* state, const void* req_meta, const void* slots,
@@ -149,8 +157,12 @@ MM_EXPORT int mm_mingru_chunked(const void* a, void* y, int dtype, void* state, 
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = W >= 128 ? 128 : 64;
     const int bx = ceil_div(W, threads);
-    mm_launch(mingru_chunk_reduce_kernel, dim3(bx, n_chunks), dim3(threads), 0, s, (const float*)a, (float*)A, (float*)B,
-              (const int32_t*)chunk_meta, (const float*)bias, W);
+    if (dtype == MM_BF16)
+        mm_launch(mingru_chunk_reduce_kernel<true>, dim3(bx, n_chunks), dim3(threads), 0, s, (const float*)a, (float*)A, (float*)B,
+                  (const int32_t*)chunk_meta, (const float*)bias, W);
+    else
+        mm_launch(mingru_chunk_reduce_kernel<false>, dim3(bx, n_chunks), dim3(threads), 0, s, (const float*)a, (float*)A, (float*)B,
+                  (const int32_t*)chunk_meta, (const float*)bias, W);
     MM_CHECK_LAUNCH();
     mm_launch(mingru_chunk_carry_kernel, dim3(bx, n_requests), dim3(threads), 0, s, (const float*)A, (float*)B, (float*)state,
               (const int32_t*)req_chunks, (const int32_t*)chunk_meta, (const int32_t*)slots, (const int32_t*)positions, W);

@@ -294,12 +294,13 @@ def test_mingru_walk_and_chunked_scan(dtype):
     positions = np.concatenate([np.arange(p, p + ln) for p, ln in zip(first_pos, lens)]).astype(np.int32)
     meta = np.stack([starts, lens, np.zeros(4), slots], 1).astype(np.int32)
     tol = 3e-6 if dtype == "float32" else 1e-2
+    state_tol = 3e-6 if dtype == "float32" else 3e-5          # bfloat16 runs take the hardware's exponential and reciprocal
     # the walk
     state = dev(state0)
     y = torch.empty((n, W), dtype=DT[dtype], device=DEV)
     ops.mingru_walk(dev(a), y, state, dev(meta, torch.int32), dev(slots, torch.int32), dev(positions, torch.int32), 4, dev(bias))
     assert np.abs(y.float().cpu().numpy() - want_y).max() <= tol * np.abs(want_y).max()
-    assert np.abs(state.cpu().numpy() - want_state).max() <= 3e-6 * np.abs(want_state).max()
+    assert np.abs(state.cpu().numpy() - want_state).max() <= state_tol * np.abs(want_state).max()
     # the scan over chunks
 
     class Ctx:
@@ -311,7 +312,7 @@ def test_mingru_walk_and_chunked_scan(dtype):
     y2 = torch.empty((n, W), dtype=DT[dtype], device=DEV)
     ops.mingru_chunked(dev(a), y2, state, chunk_meta, req_chunks, dev(slots, torch.int32), dev(positions, torch.int32), dev(bias))
     assert np.abs(y2.float().cpu().numpy() - want_y).max() <= tol * np.abs(want_y).max()
-    assert np.abs(state.cpu().numpy() - want_state).max() <= 3e-6 * np.abs(want_state).max()
+    assert np.abs(state.cpu().numpy() - want_state).max() <= state_tol * np.abs(want_state).max()
     # one token per request without a request table (a decode batch): request r is token r
     state = dev(state0)
     a1 = a[:4]
