@@ -101,6 +101,19 @@ __device__ __forceinline__ float ld_peer_f32(const float* local, uint32_t rank) 
     return v;
 }
 
+// A softmax sink (a key of score 0 without a value) joins a row's finished sums, which are relative to the maximum mu
+// (in units of log2): its weight is 2^(-mu).  For a negative mu the sums are brought to the sink's scale instead, so
+// that nothing overflows.
+__device__ __forceinline__ void add_sink(float mu, float& l, float& acc) {
+    if (mu < 0.0f) {
+        const float f = exp2f(mu);
+        l = l * f + 1.0f;
+        acc *= f;
+    } else {
+        l += exp2f(-mu);
+    }
+}
+
 template <int HD, int STAGES, bool CLUSTER>
 __global__ void __launch_bounds__(DT_THREADS)
 attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -108,7 +121,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
                             float* __restrict__ part_ml, const int32_t* __restrict__ items, const int32_t* __restrict__ positions,
                             const int32_t* __restrict__ token_req, const int32_t* __restrict__ block_table, int table_width,
                             int page_size, int H, int G, int window, float scale_log2, int split_len, int max_splits,
-                            int* __restrict__ err) {
+                            int sink, int* __restrict__ err) {
     constexpr int KSTEPS = HD / 16;
     constexpr int NT_O = HD / 8;
     constexpr int HALVES = HD / 64;
@@ -353,6 +366,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
                 fin_ml[r * 2 + 1] = l;
             }
         } else if (single) {
+            if (sink) add_sink(mu, l, acc);
             out[((size_t)t * H + h) * HD + col] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
         } else {
             const size_t p = ((size_t)item * H + h) * max_splits + split;
@@ -390,6 +404,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
                     acc += ld_peer_f32(&fin_o[r * HD + col], sI) * f;
                 }
             }
+            if (sink) add_sink(mu, l, acc);
             out[((size_t)t * H + g * qpg + r) * HD + col] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
         }
         cluster_sync_all();                            // peers may still be reading this CTA's shared memory
@@ -400,7 +415,7 @@ template <int HD, int STAGES, bool CLUSTER>
 int launch_decode_tma(const CUtensorMap& tk, const CUtensorMap& tv, const void* q, void* out, void* part_o, void* part_ml,
                       const void* items, int n_items, const void* positions, const void* token_req, const void* table,
                       int table_width, int page_size, int H, int G, int window, float scale, int split_len, int max_splits,
-                      int* err, cudaStream_t s) {
+                      int sink, int* err, cudaStream_t s) {
     constexpr int TILE = DT_KT * HD * 2;
     const size_t smem = (size_t)2 * STAGES * TILE + sizeof(DecCtl<STAGES>);
     static bool configured = false;
@@ -426,7 +441,7 @@ int launch_decode_tma(const CUtensorMap& tk, const CUtensorMap& tv, const void* 
     cudaLaunchKernelEx(&cfg, attention_decode_tma_kernel<HD, STAGES, CLUSTER>, tk, tv, (const __nv_bfloat16*)q, (__nv_bfloat16*)out,
                        (float*)part_o, (float*)part_ml, (const int32_t*)items, (const int32_t*)positions, (const int32_t*)token_req,
                        (const int32_t*)table, table_width, page_size, H, G, window, scale * 1.4426950408889634f, split_len,
-                       max_splits, err);
+                       max_splits, sink, err);
     MM_CHECK_LAUNCH();
     return MM_OK;
 }
@@ -465,11 +480,11 @@ int max_active_clusters(int cluster_size, int* out) {
 // (mm_attention_decode_merge_bf16), unless `cluster` is set: then 2 <= max_splits <= 8, the splits are merged inside the
 // kernel by a thread-block cluster, no scratch is used and `out` is final.
 // Arguments as mm_attention_decode_bf16, plus the pool size for the tensor maps.
-MM_EXPORT int mm_attention_decode_tma_bf16(const void* q, const void* k_pages, const void* v_pages, void* out, void* part_o,
-                                           void* part_ml, const void* items, int n_items, const void* positions,
-                                           const void* token_req, const void* block_table, int table_width, int page_size,
-                                           int num_pages, int H, int G, int hd, int window, float scale, int split_len,
-                                           int max_splits, int stages, int cluster, void* err, void* stream) {
+static int attention_decode_tma_launch(const void* q, const void* k_pages, const void* v_pages, void* out, void* part_o,
+                                       void* part_ml, const void* items, int n_items, const void* positions,
+                                       const void* token_req, const void* block_table, int table_width, int page_size,
+                                       int num_pages, int H, int G, int hd, int window, float scale, int split_len,
+                                       int max_splits, int stages, int cluster, int sink, void* err, void* stream) {
     MM_REQUIRE(hd == 64 || hd == 128, "attention_decode_tma: built for head_dim 64 and 128");
     MM_REQUIRE(n_items >= 0 && H > 0 && G > 0 && H % G == 0 && H / G <= 16 && num_pages > 0, "attention_decode_tma: bad head counts");
     MM_REQUIRE(page_size >= 8 && page_size <= 64 && (64 % page_size) == 0, "attention_decode_tma: page_size must be 8, 16, 32 or 64");
@@ -486,11 +501,33 @@ MM_EXPORT int mm_attention_decode_tma_bf16(const void* q, const void* k_pages, c
     }
     cudaStream_t s = (cudaStream_t)stream;
 #define MM_DT(HDV, ST, CL) launch_decode_tma<HDV, ST, CL>(tk, tv, q, out, part_o, part_ml, items, n_items, positions, token_req, block_table, \
-                                                          table_width, page_size, H, G, window, scale, split_len, max_splits, (int*)err, s)
+                                                          table_width, page_size, H, G, window, scale, split_len, max_splits, sink, (int*)err, s)
     if (cluster) return hd == 128 ? MM_DT(128, 3, true) : MM_DT(64, 3, true);
     if (hd == 128) return stages == 3 ? MM_DT(128, 3, false) : MM_DT(128, 6, false);
     return stages == 3 ? MM_DT(64, 3, false) : MM_DT(64, 6, false);
 #undef MM_DT
+}
+
+MM_EXPORT int mm_attention_decode_tma_bf16(const void* q, const void* k_pages, const void* v_pages, void* out, void* part_o,
+                                           void* part_ml, const void* items, int n_items, const void* positions,
+                                           const void* token_req, const void* block_table, int table_width, int page_size,
+                                           int num_pages, int H, int G, int hd, int window, float scale, int split_len,
+                                           int max_splits, int stages, int cluster, void* err, void* stream) {
+    return attention_decode_tma_launch(q, k_pages, v_pages, out, part_o, part_ml, items, n_items, positions, token_req, block_table,
+                                       table_width, page_size, num_pages, H, G, hd, window, scale, split_len, max_splits, stages,
+                                       cluster, 0, err, stream);
+}
+
+// The same with a softmax sink (one added to every row's denominator), for the two forms that finish a row inside the
+// kernel: one split per token, or the splits of a token as one cluster.
+MM_EXPORT int mm_attention_decode_tma_bf16_sink(const void* q, const void* k_pages, const void* v_pages, void* out, const void* items,
+                                                int n_items, const void* positions, const void* token_req, const void* block_table,
+                                                int table_width, int page_size, int num_pages, int H, int G, int hd, int window,
+                                                float scale, int max_splits, int cluster, int sink, void* err, void* stream) {
+    MM_REQUIRE(cluster || max_splits == 1, "attention_decode_tma: with a sink the splits of a token are one cluster");
+    return attention_decode_tma_launch(q, k_pages, v_pages, out, nullptr, nullptr, items, n_items, positions, token_req, block_table,
+                                       table_width, page_size, num_pages, H, G, hd, window, scale, 0, max_splits, 3, cluster, sink, err,
+                                       stream);
 }
 
 // Clusters of `cluster_size` (2..8) CTAs of the cluster variant that fit on the current device at the same time; a

@@ -23,6 +23,7 @@ def paged_attention(q, cache, out, ctx, num_heads: int, num_kv_heads: int, head_
                                  cache.block_table, cache.page_size, num_heads, num_kv_heads, head_dim, window, scale)
 
 
+USE_SINK_TMA_DECODE = True   # False: single tokens never take the TMA decode kernel
 USE_SINK_TCGEN05 = True    # False: portions never take the tcgen05 prefill kernel (tests compare it with the mma.sync one)
 USE_SINK_MMA = True        # False: the sink attention always runs the fp32-arithmetic kernel (tests compare the two)
 SINK_PREFILL_MIN = 16      # shorter portions go token by token through the decode kernel
@@ -39,6 +40,7 @@ def _sink_lib():
         _lib.declare("mm_attention_sink_supported", [I, I])
         _lib.declare("mm_attention_sink_prefill_bf16", [P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, P])
         _lib.declare("mm_attention_sink_decode_bf16", [P, P, P, P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P])
+        _lib.declare("mm_attention_decode_tma_bf16_sink", [P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, P])
         _lib.declare("mm_attention_prefill_tcgen05_sink", [P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, F, I, P, P])
         _sink_declared = True
     return _lib.load()
@@ -107,7 +109,22 @@ def paged_sink_attention(q, cache, out, ctx, num_heads: int, num_kv_heads: int, 
                                                      n_tiles, table.data_ptr(), table.shape[1], cache.page_size, num_heads, num_kv_heads,
                                                      key_dim, value_dim, int(window), float(scale), int(bool(sink)), stream),
                   "attention_sink_prefill_bf16")
-        if n_items:
+        tma = None
+        if n_items and USE_SINK_TMA_DECODE and key_dim == value_dim and key_dim in (64, 128) and cache.page_size in (8, 16, 32, 64):
+            # equal key and value sizes of 64 or 128: the TMA decode kernel of the plain attention, in the forms that
+            # finish a row inside the kernel (one split, or the splits of a token as one cluster)
+            keys = min(window, ctx.max_kv_len) if window > 0 else ctx.max_kv_len
+            _len, max_splits, cluster = attention_bf16.choose_split(n_items, num_kv_heads, keys, key_dim, cache.page_size)
+            if cluster or max_splits == 1:
+                tma = (max_splits, cluster)
+        if tma is not None:
+            check(lib.mm_attention_decode_tma_bf16_sink(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(),
+                                                        items.data_ptr() if items is not None else None, n_items, ctx.positions.data_ptr(),
+                                                        ctx.token_req.data_ptr(), table.data_ptr(), table.shape[1], cache.page_size,
+                                                        k_pages.shape[0], num_heads, num_kv_heads, key_dim, int(window), float(scale),
+                                                        tma[0], int(tma[1]), int(bool(sink)), ops.tcgen05_error_flag(q.device).data_ptr(), stream),
+                  "attention_decode_tma_bf16_sink")
+        elif n_items:
             splits = sink_splits(n_items, num_kv_heads, window, ctx.max_kv_len)
             part_o = part_ml = None
             if splits > 1:

@@ -133,6 +133,7 @@ def test_sink_attention_against_the_plain_one(H, G, dk, dv, window, page, dtype,
         pytest.skip("the tcgen05 prefill kernel takes equal key and value sizes of 64 or 128")
     monkeypatch.setattr(attention, "USE_SINK_MMA", kernels != "plain")
     monkeypatch.setattr(attention, "USE_SINK_TCGEN05", kernels == "tcgen05")
+    monkeypatch.setattr(attention, "USE_SINK_TMA_DECODE", kernels == "tcgen05")
     from mimirmind_b200.parts.base import LayerCache
     rng = np.random.RandomState(H * 100 + dk)
     T, scale = 300, 0.37 / np.sqrt(dk) * 4
