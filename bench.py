@@ -177,12 +177,12 @@ COMPARE_SIZES = {
 
 def bigerax_config(z):
     att = {"type": "attention", "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"],
-                                          "scale": z["dim"] ** -0.5, "mask": {"size": z["window"]}, "rot": {"dims": z["dim"], "base": 500000.0},
+                                          "scale": z["dim"] ** -0.5, "mask": {"size": z["window"]}, "rot": {"dims": z["dim"], "base": 10000.0},
                                           "v_mix": True}, "mlp": {"kind": "dense", "ff": z["ff"]}}
     gru = {"type": "mingru", "mixer": {"width": z["gru"]}, "mlp": None}
     layers = [gru if i % 4 == 3 else att for i in range(z["layers"])]
     return {"architecture": "Bigerax", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6, "groups": 2},
-            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}}, "layers": layers}
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 33, "mul_cur": 7}}, "layers": layers}
 
 
 def qwen2_config(z, context):

@@ -37,9 +37,9 @@ CONFIGS = {
     ]),
     # one norm group, a width that the weight-streaming product of a few rows takes, keys and values of one size, one kv head
     "Q": config(320, 256, 1, 1e-6, 64, 3, 5, [
-        attention(4, 1, 64, 64, window=50, rot=(64, 500000.0), v_mix=True, ff=256),
+        attention(4, 1, 64, 64, window=50, rot=(64, 250000.0), v_mix=True, ff=256),
         mingru(256, ff=512),
-        attention(4, 1, 64, 64, window=50, rot=(64, 500000.0), v_mix=True),
+        attention(4, 1, 64, 64, window=50, rot=(64, 250000.0), v_mix=True),
     ]),
     # sizes that fit no tile: odd width per group, odd key size with an even rotated part, a vocabulary of 77
     "R": config(77, 54, 3, 1e-6, 11, 1, 1, [
@@ -52,7 +52,7 @@ CONFIGS = {
     # and are not multiples of a key tile, eight query heads on two kv heads
     "S": config(200, 128, 2, 1e-6, 97, 5, 3, [
         attention(4, 2, 32, 64, window=64, rot=(32, 10000.0), v_mix=True, ff=192),
-        attention(8, 2, 96, 32, window=45, rot=(64, 500000.0), v_mix=False, ff=128),
+        attention(8, 2, 96, 32, window=45, rot=(64, 250000.0), v_mix=False, ff=128),
         mingru(96),
         attention(4, 2, 32, 64, window=130, rot=(16, 10000.0), v_mix=True),
     ]),

@@ -121,7 +121,7 @@ def _paged(k, v, page_size, rng, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,G,dk,dv,window,page", [(4, 2, 24, 16, 19, 16), (3, 3, 9, 7, 40, 8), (8, 1, 64, 64, 0, 16), (4, 4, 96, 32, 33, 32),
+@pytest.mark.parametrize("H,G,dk,dv,window,page", [(4, 2, 24, 16, 19, 16), (3, 3, 9, 7, 40, 8), (8, 1, 64, 64, 0, 16), (4, 4, 96, 64, 33, 32),
                                                    (2, 1, 128, 128, 130, 16), (2, 2, 16, 200, 5, 16), (16, 1, 32, 96, 100, 16),
                                                    (6, 2, 128, 64, 0, 64)])
 @pytest.mark.parametrize("kernels", ["tcgen05", "mma", "plain"])
@@ -223,8 +223,8 @@ def test_one_key_that_stands_out_is_seen_exactly_inside_the_window(window, page,
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,G,dk,dv,rots", [(3, 2, 10, 6, ((10, 10000.0), (4, 500000.0), (0, 1.0))),
-                                            (4, 2, 32, 16, ((32, 10000.0), (8, 500000.0), (0, 1.0))),      # 16-byte chunks
+@pytest.mark.parametrize("H,G,dk,dv,rots", [(3, 2, 10, 6, ((10, 10000.0), (4, 250000.0), (0, 1.0))),
+                                            (4, 2, 32, 16, ((32, 10000.0), (8, 250000.0), (0, 1.0))),      # 16-byte chunks
                                             (2, 1, 96, 32, ((64, 300.0), (12, 10000.0)))])
 def test_pair_rotation_value_mixing_and_cache_write_sizes(H, G, dk, dv, rots, dtype):
     _pair_rotation_case(H, G, dk, dv, rots, dtype)
