@@ -84,10 +84,10 @@ class _At:
             raise ConfigError(f"{self.where}: missing required key '{self._name(key)}'")
         return self.obj[key]
 
-    def integer(self, key: str, minimum: int = 1) -> int:
+    def integer(self, key: str, minimum: Optional[int] = 1) -> int:
         v = self.need(key)
-        if isinstance(v, bool) or not isinstance(v, int) or v < minimum:
-            raise ConfigError(f"{self.where}: '{self._name(key)}' must be an integer >= {minimum}, got {v!r}")
+        if isinstance(v, bool) or not isinstance(v, int) or (minimum is not None and v < minimum):
+            raise ConfigError(f"{self.where}: '{self._name(key)}' must be an integer" + (f" >= {minimum}" if minimum is not None else "") + f", got {v!r}")
         return v
 
     def number(self, key: str) -> float:
@@ -147,6 +147,6 @@ def parse_bigerax_config(obj: Dict[str, Any], where: str = "config.json") -> Big
     max_pos = obj.get("max_positions")
     return BigeraxConfig(
         architecture=str(obj.get("architecture", ARCHITECTURE)), vocab=top.integer("vocab"), width=width,
-        buckets=big.integer("buckets"), mul_prev=big.integer("mul_prev", 0), mul_cur=big.integer("mul_cur", 0),
+        buckets=big.integer("buckets"), mul_prev=big.integer("mul_prev", None), mul_cur=big.integer("mul_cur", None),
         norm_eps=norm.number("eps"), norm_groups=groups, layers=tuple(layers),
         max_positions=int(max_pos) if isinstance(max_pos, int) and max_pos > 0 else 1 << 20, eos_token_ids=eos_ids)

@@ -69,10 +69,11 @@ def test_group_norm_chain(d, groups, dtype):
         assert torch.equal(a[:, d // groups:], b[:, d // groups:])
 
 
-def test_bigram_embedding_carries_the_previous_token_in_its_slot():
+@pytest.mark.parametrize("d,mp,mc", [(24, 29, 13), (20, -7, 5), (7, 1, 1), (24, 2 ** 40 + 3, 2 ** 35 + 1)])
+def test_bigram_embedding_carries_the_previous_token_in_its_slot(d, mp, mc):
     from mimirmind_b200.kernels import ops
     rng = np.random.RandomState(3)
-    V, d, B, mp, mc = 50, 24, 13, 31, 17
+    V, B = 50, 13
     table, pairs = bf16_round(rng.randn(V, d)), bf16_round(rng.randn(B + 1, d))
     state = torch.full((4,), 7, dtype=torch.int32, device=DEV)          # what an earlier user of the slots left behind
 
