@@ -9,6 +9,8 @@
 #include "exec.h"
 #include "kernels_api.h"
 
+void mm_set_last_error(const char* msg);       // host.cu: the kernel library's error text (mm_last_error)
+
 namespace mmx {
 
 void check_kernel(int code, const char* what) {
@@ -132,7 +134,7 @@ struct Blas::Impl {
         cublasLtMatrixLayout_t a = nullptr, b = nullptr, c = nullptr;
         cublasLtMatmulAlgo_t algo;
     };
-    std::map<std::tuple<int, int, int, int>, Plan> plans;
+    std::map<std::tuple<int, int, int, int, int>, Plan> plans;     // (M, N, K, out dtype, with bias)
 
     template <typename F>
     void sym(F& f, const char* name) {
@@ -182,9 +184,9 @@ Blas::~Blas() {
     if (m.workspace) cudaFree(m.workspace);
 }
 
-void Blas::gemm_nt(const void* x, const void* W, void* out, int out_dtype, int M, int N, int K, cudaStream_t s) {
+void Blas::gemm_nt(const void* x, const void* W, void* out, int out_dtype, int M, int N, int K, cudaStream_t s, const void* bias) {
     Impl& m = *impl_;
-    auto key = std::make_tuple(M, N, K, out_dtype);
+    auto key = std::make_tuple(M, N, K, out_dtype, bias ? 1 : 0);
     auto it = m.plans.find(key);
     if (it == m.plans.end()) {
         // Row-major out[M, N] = x[M, K] W[N, K]^T is, in the library's column-major terms, out^T[N, M] = W'[K, N]^T x'[K, M]
@@ -194,6 +196,13 @@ void Blas::gemm_nt(const void* x, const void* W, void* out, int out_dtype, int M
         m.ck(m.desc_set(p.op, CUBLASLT_MATMUL_DESC_TRANSA, &ta, sizeof(ta)), "set TRANSA");
         m.ck(m.desc_set(p.op, CUBLASLT_MATMUL_DESC_TRANSB, &tb, sizeof(tb)), "set TRANSB");
         const cudaDataType_t ct = out_dtype == F32 ? CUDA_R_32F : CUDA_R_16BF;
+        if (bias) {
+            // out^T[N, M] gets bias[n] added to row n: the library's bias epilogue, the vector in the output's type
+            cublasLtEpilogue_t epi = CUBLASLT_EPILOGUE_BIAS;
+            m.ck(m.desc_set(p.op, CUBLASLT_MATMUL_DESC_EPILOGUE, &epi, sizeof(epi)), "set EPILOGUE");
+            m.ck(m.desc_set(p.op, CUBLASLT_MATMUL_DESC_BIAS_DATA_TYPE, &ct, sizeof(ct)), "set BIAS_DATA_TYPE");
+            m.ck(m.desc_set(p.op, CUBLASLT_MATMUL_DESC_BIAS_POINTER, &bias, sizeof(bias)), "set BIAS_POINTER");
+        }
         m.ck(m.layout_create(&p.a, CUDA_R_16BF, K, N, K), "layout A");
         m.ck(m.layout_create(&p.b, CUDA_R_16BF, K, M, K), "layout B");
         m.ck(m.layout_create(&p.c, ct, N, M, N), "layout C");
@@ -211,7 +220,24 @@ void Blas::gemm_nt(const void* x, const void* W, void* out, int out_dtype, int M
     }
     const Impl::Plan& p = it->second;
     const float one = 1.f, zero = 0.f;
+    if (bias) m.ck(m.desc_set(p.op, CUBLASLT_MATMUL_DESC_BIAS_POINTER, &bias, sizeof(bias)), "set BIAS_POINTER");
     m.ck(m.matmul(m.handle, p.op, &one, W, p.a, x, p.b, &zero, out, p.c, out, p.c, &p.algo, m.workspace, m.workspace_bytes, s), "Matmul");
+}
+
+// The same product for callers outside the executor (the Python part classes): one instance per process, made at the
+// first call.  bias (or null): [N] in the output's dtype, added by the library's epilogue.
+extern "C" __attribute__((visibility("default"))) int mm_blas_gemm_nt(const void* x, const void* W, const void* bias, void* out,
+                                                                      int out_dtype, int M, int N, int K, void* stream) {
+    static std::unique_ptr<Blas> blas;
+    try {
+        if (M <= 0 || N <= 0 || K <= 0 || (out_dtype != F32 && out_dtype != BF16)) throw ExecError("blas product: bad sizes or output dtype");
+        if (!blas) blas.reset(new Blas());
+        blas->gemm_nt(x, W, out, out_dtype, M, N, K, (cudaStream_t)stream, bias);
+        return 0;
+    } catch (const std::exception& e) {
+        ::mm_set_last_error(e.what());
+        return 4;
+    }
 }
 
 // ---- dispatch ---------------------------------------------------------------------------------------------------------

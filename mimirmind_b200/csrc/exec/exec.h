@@ -251,8 +251,8 @@ class Blas {
   public:
     Blas();
     ~Blas();
-    // out[M, N] (bf16 or fp32) = x[M, K] (bf16) * W[N, K]^T (bf16), fp32 accumulation
-    void gemm_nt(const void* x, const void* W, void* out, int out_dtype, int M, int N, int K, cudaStream_t s);
+    // out[M, N] (bf16 or fp32) = x[M, K] (bf16) * W[N, K]^T (bf16) (+ bias[N] in the output's dtype), fp32 accumulation
+    void gemm_nt(const void* x, const void* W, void* out, int out_dtype, int M, int N, int K, cudaStream_t s, const void* bias = nullptr);
 
   private:
     struct Impl;

@@ -76,9 +76,19 @@ def sink_plan(ctx, n_tokens: int, tile_rows: int = SINK_TILE_ROWS):
                 items.extend(range(s, s + n))
         tiles.sort(key=lambda tile: tile[3] + tile[2])
         device = ctx.positions.device
-        d_tiles = torch.tensor(tiles, dtype=torch.int32, device=device) if tiles else None
-        d_items = None if len(items) == n_tokens or not items else torch.tensor(items, dtype=torch.int32, device=device)
+        # from pinned memory, without waiting: a copy from pageable memory would hold the host until the device has
+        # caught up, and the layers after it would be launched into an empty queue
+        staged = []
+
+        def to_device(rows):
+            host = torch.tensor(rows, dtype=torch.int32).pin_memory()
+            staged.append(host)
+            return host.to(device, non_blocking=True)
+
+        d_tiles = to_device(tiles) if tiles else None
+        d_items = None if len(items) == n_tokens or not items else to_device(items)
         plan = ctx.plans[key] = (d_tiles, len(tiles), d_items, len(items))
+        ctx.plans[key + ("staged",)] = staged                  # the pinned copies live as long as the step's context
     return plan
 
 

@@ -61,8 +61,11 @@ class MinGRU(Mixer):
                     meta.append((s + off, min(CHUNK, n - off), r, int(off == 0)))
                 per_req.append((first, len(meta) - first))
             host = np.concatenate([np.asarray(meta, dtype=np.int32).reshape(-1), np.asarray(per_req, dtype=np.int32).reshape(-1)])
-            dev = torch.from_numpy(host).to(ctx.token_ids.device)
+            # from pinned memory, without waiting for the device (a pageable copy would stall the launches behind it)
+            pinned = torch.from_numpy(host).pin_memory()
+            dev = pinned.to(ctx.token_ids.device, non_blocking=True)
             ctx.derived[key] = (dev[:4 * len(meta)].view(len(meta), 4), dev[4 * len(meta):].view(len(per_req), 2))
+            ctx.derived[key + ("staged",)] = pinned
         return ctx.derived[key]
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
