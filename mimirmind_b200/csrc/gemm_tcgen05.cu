@@ -69,6 +69,16 @@ struct SharedCtl {
 
 // The epilogue of one warp for its 32 rows (TMEM lanes) of a 128 x 256 accumulator at `taddr`: rows m0 + 32 q + lane,
 // columns n0 .. n0 + 255 of the product.
+// activations a bf16 epilogue may apply after the bias (fp32): 1 squared relu, 2 gelu (tanh form), 3 silu, 4 relu
+__device__ __forceinline__ float epilogue_activation(float z, int act) {
+    switch (act) {
+        case 1: { const float r = fmaxf(z, 0.0f); return r * r; }
+        case 2: return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+        case 3: return z / (1.0f + __expf(-z));
+        default: return fmaxf(z, 0.0f);
+    }
+}
+
 template <int EPI>
 __device__ __forceinline__ void epilogue_rows(uint32_t taddr, int m0, int n0, int q, int lane, unsigned char* wstage,
                                               void* __restrict__ out, const void* __restrict__ bias, int bias_dtype, int M,
@@ -110,11 +120,17 @@ __device__ __forceinline__ void epilogue_rows(uint32_t taddr, int m0, int n0, in
                 for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
                 unsigned char* srow = wstage + lane * 256;
                 if (EPI == EPI_BF16) {
+                    // an activation after the bias travels in the upper bits of the bias dtype (see mm_gemm_tcgen05_act)
+                    const int act = bias_dtype >> 8, bdt = bias_dtype & 0xff;
                     if (bias != nullptr) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
                             if (col0 + i < N)
-                                v[i] += (bias_dtype == MM_F32) ? ((const float*)bias)[col0 + i] : __bfloat162float(((const __nv_bfloat16*)bias)[col0 + i]);
+                                v[i] += (bdt == MM_F32) ? ((const float*)bias)[col0 + i] : __bfloat162float(((const __nv_bfloat16*)bias)[col0 + i]);
+                    }
+                    if (act != 0) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = epilogue_activation(v[i], act);
                     }
 #pragma unroll
                     for (int i = 0; i < 4; ++i)
@@ -485,6 +501,15 @@ static int gemm_tcgen05_common(const void* A, const void* W, const void* bias, i
 MM_EXPORT int mm_gemm_tcgen05(const void* A, const void* W, const void* bias, int bias_dtype, void* out, int epilogue, int M,
                               int N, int K, int lda, int ldo, void* err, void* stream) {
     return gemm_tcgen05_common(A, W, bias, bias_dtype, out, epilogue, M, N, K, lda, ldo, err, stream, false);
+}
+
+// out = act(A W^T + bias) as bf16: the plain product with an activation in its epilogue (act: 1 squared relu, 2 gelu in
+// its tanh form, 3 silu, 4 relu), on CTA pairs when `pair` is set.  The hidden rows of a two-matrix feed-forward are made
+// in one launch and never exist without their activation.
+MM_EXPORT int mm_gemm_tcgen05_act(const void* A, const void* W, const void* bias, int bias_dtype, void* out, int act, int pair, int M,
+                                  int N, int K, int lda, int ldo, void* err, void* stream) {
+    MM_REQUIRE(act >= 1 && act <= 4 && (bias_dtype == MM_F32 || bias_dtype == MM_BF16), "gemm_tcgen05: unknown activation or bias dtype");
+    return gemm_tcgen05_common(A, W, bias, bias_dtype | (act << 8), out, EPI_BF16, M, N, K, lda, ldo, err, stream, pair != 0);
 }
 
 MM_EXPORT int mm_gemm_tcgen05_pair(const void* A, const void* W, const void* bias, int bias_dtype, void* out, int epilogue, int M,

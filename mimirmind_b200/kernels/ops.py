@@ -524,6 +524,31 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
     return out
 
 
+def gemm_tcgen05_act(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], activation: str,
+                     pair: Optional[bool] = None) -> torch.Tensor:
+    """act(x[M, K] @ w[N, K]^T + bias) as bfloat16 in one launch of the tcgen05 product (the activation on the fp32
+    accumulators, in its epilogue); ``activation`` as for :func:`bias_act`."""
+    _need(x, "gemm x", torch.bfloat16)
+    _need(w, "gemm w", torch.bfloat16)
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape != (n, k) or not gemm_tcgen05_supported(m, n, k):
+        raise KernelError(f"gemm_tcgen05: shapes x{tuple(x.shape)} w{tuple(w.shape)} are not supported")
+    if activation not in ACTIVATIONS:
+        raise KernelError(f"activation '{activation}' is not one of {', '.join(sorted(ACTIVATIONS))}")
+    if bias is not None:
+        _need(bias, "gemm bias")
+        if bias.shape != (n,):
+            raise KernelError("gemm_tcgen05: bias shape mismatch")
+    out = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+    if pair is None:
+        pair = tcgen05_pair_suits(m)
+    check(_lib.load().mm_gemm_tcgen05_act(x.data_ptr(), w.data_ptr(), _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32,
+                                          out.data_ptr(), ACTIVATIONS[activation] + 1, int(pair), m, n, k, k, n,
+                                          tcgen05_error_flag(x.device).data_ptr(), _stream()), "gemm_tcgen05_act")
+    return out
+
+
 def argmax_rows(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     _need(logits, "argmax logits", torch.float32)
     r, v = logits.shape

@@ -340,6 +340,31 @@ def test_bias_and_activation(dtype):
             assert np.abs(got - want).max() <= (1e-6 if dtype == "float32" else 8e-3) * max(1.0, np.abs(want).max()), act
 
 
+@pytest.mark.parametrize("m,n,k", [(300, 512, 256), (2048, 1024, 512), (384, 264, 64), (5, 512, 256)])
+@pytest.mark.parametrize("activation", ["relu2", "gelu_tanh", "silu", "relu"])
+def test_products_with_bias_and_activation_in_their_epilogue(m, n, k, activation):
+    """The tcgen05 product (single CTAs and CTA pairs) and the weight-streaming product with the activation in their
+    epilogue against the float64 formula."""
+    from mimirmind_b200.kernels import ops
+    rng = np.random.RandomState(m + n)
+    x, w, b = bf16_round(rng.randn(m, k)), bf16_round(rng.randn(n, k) / np.sqrt(k)), bf16_round(rng.randn(n))
+    fn = {"relu2": pb.relu_squared, "relu": lambda z: np.maximum(z, 0), "silu": lambda z: z * pb.sigmoid(z),
+          "gelu_tanh": lambda z: 0.5 * z * (1 + np.tanh(np.sqrt(2 / np.pi) * (z + 0.044715 * z ** 3)))}[activation]
+    want = fn(x @ w.T + b)
+    tol = 1e-2 * max(1.0, np.abs(want).max())
+    dx, dw, db = dev(x, torch.bfloat16), dev(w, torch.bfloat16), dev(b, torch.bfloat16)
+    if m <= 8:
+        got = ops.gemv_bf16_act(dx, dw, db, activation).float().cpu().numpy()
+        assert np.abs(got - want).max() <= tol
+        return
+    for pair in (False, True):
+        got = ops.gemm_tcgen05_act(dx, dw, db, activation, pair=pair).float().cpu().numpy()
+        assert np.abs(got - want).max() <= tol, f"pair={pair}"
+    got = ops.gemm_tcgen05_act(dx, dw, None, activation).float().cpu().numpy()
+    assert np.abs(got - fn(x @ w.T)).max() <= tol
+    ops.check_tcgen05_errors(dx.device)
+
+
 # ---- whole models -------------------------------------------------------------------------------------------------------
 @pytest.fixture(scope="module")
 def models(tmp_path_factory):
