@@ -537,3 +537,18 @@ def test_the_command_line_generates_with_this_design(models, tmp_path):
                          capture_output=True, text=True, timeout=300)
     assert out.returncode == 0, out.stderr
     assert out.stdout.strip().splitlines()[1] == "generated 4"
+
+
+def test_prompt_steps_with_the_feed_forwards_fused_epilogue(models, monkeypatch):
+    """The width from which a prompt's up product takes bias and activation as its epilogue is lowered so that a small
+    model runs it: same logits as the plain implementation."""
+    from mimirmind_b200.parts import mlp
+    monkeypatch.setattr(mlp, "FUSED_UP_MIN_HIDDEN", 0)
+    folder, cfg, w = models("Q")
+    reqs = {"f0": random_tokens(cfg["vocab"], 300, 1), "f1": random_tokens(cfg["vocab"], 257, 2)}
+    ref = {rid: pb.forward(cfg, w, t) for rid, t in reqs.items()}
+    t = ru.Trace()
+    for rid, toks in reqs.items():
+        ru.whole(t, rid, toks)
+    out, _ = ru.run_in_process(folder, "bfloat16", t, t.max_live_tokens())
+    check_rows(t, out, reqs, ref, "bfloat16", "fused feed-forward epilogue")
