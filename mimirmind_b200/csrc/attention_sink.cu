@@ -4,7 +4,9 @@
 //   a query at absolute position a sees keys max(0, a + 1 - W) .. a (W = 0: all);
 //   s_j = (q . k_j) * scale;  p_j = exp(s_j) / (sink + sum_i exp(s_i)),  sink = 1 or 0;  o = sum_j p_j v_j.
 //
-// The sink is a key of score 0 that has no value: it only takes its share of the weights.
+// The sink is a key of score 0 that has no value: it only takes its share of the weights.  The fp32-arithmetic
+// kernel also takes a learned sink, exp(logit of the head) in its place, and a learned bias per (distance, head)
+// that is added to the scaled score: bias[min(a - j, rows - 1)][h] (a table by distance, clamped at its last row).
 //
 // This file holds (1) the step between the q/k/v projection and attention: rotation of adjacent pairs
 // (2i, 2i+1) of q and k by position (angles from a per-step table), the mixing of this layer's values with those of
@@ -182,7 +184,8 @@ __global__ void attention_sink_generic_kernel(const T* __restrict__ q, const T* 
                                               const T* __restrict__ v_pages, T* __restrict__ out,
                                               const int32_t* __restrict__ positions, const int32_t* __restrict__ token_req,
                                               const int32_t* __restrict__ block_table, int table_width, int page_size,
-                                              int n_tokens, int H, int G, int dk, int dv, int window, float scale, int sink) {
+                                              int n_tokens, int H, int G, int dk, int dv, int window, float scale, int sink,
+                                              const float* __restrict__ sink_logit, const float* __restrict__ dist_bias, int dist_max) {
     extern __shared__ float q_smem[];  // [warps][dk]
     const int warps_per_block = blockDim.x >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -200,8 +203,9 @@ __global__ void attention_sink_generic_kernel(const T* __restrict__ q, const T* 
     for (int d = lane; d < dk; d += 32) qs[d] = to_f32<T>(qrow[d]) * scale;
     __syncwarp();
 
-    // the sink starts the running softmax: a maximum of 0 and a mass of 1 with nothing accumulated
-    float m = sink ? 0.0f : -INFINITY, l = sink ? 1.0f : 0.0f;
+    // the sink starts the running softmax: a maximum of 0 (or of the head's learned logit) and a mass of 1 with
+    // nothing accumulated
+    float m = sink_logit ? sink_logit[h] : (sink ? 0.0f : -INFINITY), l = (sink_logit || sink) ? 1.0f : 0.0f;
     float acc[SINK_MAX_ACC];
 #pragma unroll
     for (int a = 0; a < SINK_MAX_ACC; ++a) acc[a] = 0.0f;
@@ -217,7 +221,8 @@ __global__ void attention_sink_generic_kernel(const T* __restrict__ q, const T* 
             const T* kr = k_pages + (size_t)page * k_stride + k_head + (size_t)(j % page_size) * dk;
             float dot = 0.0f;
             for (int d = 0; d < dk; ++d) dot = fmaf(qs[d], to_f32<T>(kr[d]), dot);
-            s = dot;
+            // a learned bias per (distance, head), not scaled: the table's last row stands for every larger distance
+            s = dist_bias ? dot + dist_bias[(size_t)min(pos - j, dist_max) * H + h] : dot;
         }
         const float m_new = fmaxf(m, warp_max(s));
         const float alpha = expf(m - m_new);  // m = -inf on the first chunk gives 0
@@ -251,7 +256,8 @@ __global__ void attention_sink_generic_kernel(const T* __restrict__ q, const T* 
 MM_EXPORT int mm_attention_sink_generic(const void* q, const void* k_pages, const void* v_pages, void* out, int dtype,
                                         const void* positions, const void* token_req, const void* block_table,
                                         int table_width, int page_size, int n_tokens, int H, int G, int dk, int dv, int window,
-                                        float scale, int sink, void* stream) {
+                                        float scale, int sink, const void* sink_logit, const void* dist_bias, int dist_max, void* stream) {
+    MM_REQUIRE(dist_bias == nullptr || dist_max >= 0, "attention: the distance table needs at least one row");
     MM_REQUIRE(n_tokens >= 0 && H > 0 && G > 0 && dk > 0 && dv > 0 && H % G == 0, "attention: heads must be a positive multiple of kv heads");
     MM_REQUIRE(dv <= 32 * SINK_MAX_ACC && dk <= 2048, "attention: value size above 512 or key size above 2048 is not supported");
     MM_REQUIRE(page_size > 0 && table_width > 0 && window >= 0, "attention: bad page geometry or window");
@@ -264,12 +270,13 @@ MM_EXPORT int mm_attention_sink_generic(const void* q, const void* k_pages, cons
     if (dtype == MM_F32)
         mm_launch(attention_sink_generic_kernel<float>, dim3(blocks), dim3(warps * 32), smem, s, (const float*)q, (const float*)k_pages,
                   (const float*)v_pages, (float*)out, (const int32_t*)positions, (const int32_t*)token_req,
-                  (const int32_t*)block_table, table_width, page_size, n_tokens, H, G, dk, dv, window, scale, sink);
+                  (const int32_t*)block_table, table_width, page_size, n_tokens, H, G, dk, dv, window, scale, sink,
+                  (const float*)sink_logit, (const float*)dist_bias, dist_max);
     else if (dtype == MM_BF16)
         mm_launch(attention_sink_generic_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), smem, s, (const __nv_bfloat16*)q,
                   (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, (__nv_bfloat16*)out, (const int32_t*)positions,
                   (const int32_t*)token_req, (const int32_t*)block_table, table_width, page_size, n_tokens, H, G, dk, dv, window,
-                  scale, sink);
+                  scale, sink, (const float*)sink_logit, (const float*)dist_bias, dist_max);
     else
         MM_REQUIRE(false, "attention: dtype must be float32 or bfloat16");
     MM_CHECK_LAUNCH();

@@ -283,6 +283,13 @@ MMH int mmh_st_check(void* h, const char* where, int n, const char** names, cons
         for (size_t i = 0; i < shape.size(); ++i) out += (i ? ", " : "") + std::to_string(shape[i]);
         return out + "]";
     };
+    // a wanted extent of -1 is one the file decides (a table whose number of rows no configuration key gives)
+    auto fits = [](const std::vector<long long>& file, const std::vector<long long>& wanted) {
+        if (file.size() != wanted.size()) return false;
+        for (size_t i = 0; i < file.size(); ++i)
+            if (wanted[i] != file[i] && !(wanted[i] == -1 && file[i] > 0)) return false;
+        return true;
+    };
     std::map<std::string, std::vector<long long>> want, have;
     std::map<std::string, bool> may_miss;
     size_t at = 0;
@@ -297,7 +304,7 @@ MMH int mmh_st_check(void* h, const char* where, int n, const char** names, cons
         auto it = have.find(w.first);
         if (it == have.end()) {
             if (!may_miss[w.first]) missing.push_back("    " + w.first + "  " + listed(w.second));
-        } else if (it->second != w.second) {
+        } else if (!fits(it->second, w.second)) {
             wrong.push_back("    " + w.first + ": file has " + listed(it->second) + ", config needs " + listed(w.second));
         }
     }

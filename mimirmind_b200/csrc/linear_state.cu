@@ -1,0 +1,300 @@
+// Mixers that keep a matrix per head instead of keys and values: per head, with S a [dk, dv] matrix in fp32,
+//
+//   S <- g_t S;   u_t = v_t                      (plain)      or   u_t = beta_t (v_t - S^T k_t)   (delta rule);
+//   S <- S + k_t u_t^T;   o_t = S^T q_t.
+//
+// g_t is a constant of the head (`head_decay`) or one number per token and head (`gate`).  Retention and lightning
+// attention are the plain form with a constant decay, the gated delta rule is the second form with a decay per token.
+// The state is carried per request in a state slot; a request at position 0 starts from zero whatever its slot holds.
+//
+// This file holds (1) the short causal convolution per channel whose last inputs are state too, (2) what happens to
+// q, k and v between their projection and the recurrence (activation, rotation of half-split pairs, unit length,
+// scale, and the decay per token and the write strength of the delta rule), all in fp32 and in place, and (3) the recurrence as a
+// walk over each request's tokens.  Columns of S are independent of one another: a thread owns an eighth of one
+// column (its entries i = 8e + lane%8), eight lanes add up the two dot products of a token, and a block of 128
+// threads walks 16 columns of one head.  The layout of the state in a slot is [H, dv, dk]: what a warp reads is one run.
+#include "common.cuh"
+
+#define LS_MAX_TAPS 8
+#define LS_AHEAD 16      // tokens staged in shared memory per round
+#define LS_COLS 16       // columns of S per block
+
+__device__ __forceinline__ float ls_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float ls_silu(float x) { return x * ls_sigmoid(x); }
+__device__ __forceinline__ float ls_softplus(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
+
+// ---------------------------------------------------------------------------------------------------------------
+// short causal convolution over time, per channel, in place: y_t = act(sum_j taps[c][K-1-j] x_(t-j))
+// ---------------------------------------------------------------------------------------------------------------
+// x [n, ld] fp32 (the first C columns are convolved), taps [C, K] fp32 (last column: the current token), tail
+// [slots, tail_stride] fp32 with the request's last K-1 inputs at [j * C + c], j = 0 the most recent.  One thread
+// per (request, channel) walks the request's tokens with the last inputs in registers.
+__global__ void causal_conv_walk_kernel(float* __restrict__ x, int ld, int C, const float* __restrict__ taps, int K,
+                                        float* __restrict__ tail, long long tail_stride, const int32_t* __restrict__ req_meta,
+                                        const int32_t* __restrict__ slots, const int32_t* __restrict__ positions, int act) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int r = blockIdx.y;
+    if (c >= C) return;
+    const int t0 = req_meta ? req_meta[4 * r] : r;
+    const int n = req_meta ? req_meta[4 * r + 1] : 1;
+    float* tl = tail + (size_t)slots[r] * tail_stride;
+    const bool fresh = positions[t0] == 0;
+    float w[LS_MAX_TAPS], win[LS_MAX_TAPS];      // win[j]: the input j+1 tokens back
+#pragma unroll
+    for (int j = 0; j < LS_MAX_TAPS; ++j) {
+        w[j] = j < K ? taps[(size_t)c * K + (K - 1 - j)] : 0.0f;      // w[j] multiplies the input j tokens back
+        win[j] = (j < K - 1 && !fresh) ? tl[(size_t)j * C + c] : 0.0f;
+    }
+    for (int t = t0; t < t0 + n; ++t) {
+        float* p = x + (size_t)t * ld + c;
+        const float cur = *p;
+        float y = w[0] * cur;
+#pragma unroll
+        for (int j = 1; j < LS_MAX_TAPS; ++j) y = fmaf(w[j], win[j - 1], y);
+#pragma unroll
+        for (int j = LS_MAX_TAPS - 1; j > 0; --j) win[j] = win[j - 1];
+        win[0] = cur;
+        *p = act ? ls_silu(y) : y;
+    }
+#pragma unroll
+    for (int j = 0; j < LS_MAX_TAPS; ++j)
+        if (j < K - 1) tl[(size_t)j * C + c] = win[j];
+}
+
+MM_EXPORT int mm_causal_conv_walk(void* x, int ld, int C, const void* taps, int K, void* tail, long long tail_stride,
+                                  const void* req_meta, const void* slots, const void* positions, int n_requests, int act, void* stream) {
+    MM_REQUIRE(C > 0 && ld >= C && K >= 1 && K <= LS_MAX_TAPS, "causal conv: 1 to 8 taps, and at least as many columns as channels");
+    MM_REQUIRE(tail != nullptr && slots != nullptr && positions != nullptr, "causal conv: the state and the positions are needed");
+    if (n_requests <= 0) return MM_OK;
+    mm_launch(causal_conv_walk_kernel, dim3(ceil_div(C, 128), n_requests), dim3(128), 0, (cudaStream_t)stream, (float*)x, ld, C,
+              (const float*)taps, K, (float*)tail, tail_stride, (const int32_t*)req_meta, (const int32_t*)slots, (const int32_t*)positions, act);
+    MM_CHECK_LAUNCH();
+    return MM_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// between projection and recurrence, in place on the fp32 rows of the projection
+// ---------------------------------------------------------------------------------------------------------------
+// Row t of x holds q at q_off (Gq heads of dk), k at k_off (Gq heads of dk) and v at v_off (n_v numbers).  In this
+// order: act (1: silu on q, k and v); rotation of the pairs (i, i + rot_dims/2) of every q and k head by the angles
+// of rot[t] (cos, sin per pair; made from the positions once per step); unit length (x / sqrt(sum x^2 + unit_eps))
+// when `unit`; q *= q_scale, k *= k_scale.  With a_off >= 0 also a decay per token and head,
+// gate = exp(-exp(A_log) softplus(a + dt_bias)), and with b_off >= 0 the delta rule's write strength, beta = sigmoid(b),
+// from the columns a_off.. and b_off.. of the row.
+__global__ void linear_state_prep_kernel(float* __restrict__ x, int ld, int q_off, int k_off, int v_off, int Gq, int dk, int n_v,
+                                         int act, const float2* __restrict__ rot, int rot_dims, int unit, float unit_eps,
+                                         float q_scale, float k_scale, int a_off, int b_off, int H, const float* __restrict__ A_log,
+                                         const float* __restrict__ dt_bias, float* __restrict__ gate, float* __restrict__ beta) {
+    const int t = blockIdx.x;
+    float* row = x + (size_t)t * ld;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int half = rot_dims / 2;
+    for (int vec = warp; vec < 2 * Gq; vec += warps) {
+        const bool is_q = vec < Gq;
+        float* p = row + (is_q ? q_off + vec * dk : k_off + (vec - Gq) * dk);
+        if (act)
+            for (int d = lane; d < dk; d += 32) p[d] = ls_silu(p[d]);
+        __syncwarp();
+        if (rot_dims) {
+            const float2* cs = rot + (size_t)t * half;
+            for (int i = lane; i < half; i += 32) {
+                const float a = p[i], b = p[i + half];
+                p[i] = a * cs[i].x - b * cs[i].y;
+                p[i + half] = b * cs[i].x + a * cs[i].y;
+            }
+            __syncwarp();
+        }
+        float f = is_q ? q_scale : k_scale;
+        if (unit) {
+            float ss = 0.0f;
+            for (int d = lane; d < dk; d += 32) ss = fmaf(p[d], p[d], ss);
+            ss = warp_sum(ss);
+            f *= 1.0f / sqrtf(ss + unit_eps);
+        }
+        if (f != 1.0f)
+            for (int d = lane; d < dk; d += 32) p[d] *= f;
+    }
+    if (act)
+        for (int d = threadIdx.x; d < n_v; d += blockDim.x) row[v_off + d] = ls_silu(row[v_off + d]);
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        if (a_off >= 0) gate[(size_t)t * H + h] = expf(-expf(A_log[h]) * ls_softplus(row[a_off + h] + dt_bias[h]));
+        if (b_off >= 0) beta[(size_t)t * H + h] = ls_sigmoid(row[b_off + h]);
+    }
+}
+
+MM_EXPORT int mm_linear_state_prep(void* x, int ld, int n_tokens, int q_off, int k_off, int v_off, int Gq, int dk, int n_v, int act,
+                                   const void* rot, int rot_dims, int unit, float unit_eps, float q_scale, float k_scale, int a_off,
+                                   int b_off, int H, const void* A_log, const void* dt_bias, void* gate, void* beta, void* stream) {
+    MM_REQUIRE(n_tokens >= 0 && Gq > 0 && dk > 0 && n_v >= 0 && ld > 0, "linear state prep: bad sizes");
+    MM_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dk && (rot_dims == 0 || rot != nullptr), "linear state prep: the rotated dimensions must be even, at most the head size, and have their table");
+    MM_REQUIRE(a_off < 0 || (H > 0 && A_log && dt_bias && gate), "linear state prep: the decay per token needs its inputs and its output");
+    MM_REQUIRE(b_off < 0 || (H > 0 && beta), "linear state prep: the write strength needs its output");
+    if (a_off < 0 && b_off < 0) H = 0;
+    if (n_tokens == 0) return MM_OK;
+    mm_launch(linear_state_prep_kernel, dim3(n_tokens), dim3(128), 0, (cudaStream_t)stream, (float*)x, ld, q_off, k_off, v_off, Gq, dk, n_v, act,
+              (const float2*)rot, rot_dims, unit, unit_eps, q_scale, k_scale, a_off, b_off, H, (const float*)A_log, (const float*)dt_bias,
+              (float*)gate, (float*)beta);
+    MM_CHECK_LAUNCH();
+    return MM_OK;
+}
+
+// (cos, sin) of position * freq[i] for every token and pair, fp32
+__global__ void angle_table_kernel(const int32_t* __restrict__ positions, const float* __restrict__ freq, float2* __restrict__ table,
+                                   int n_tokens, int half) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)n_tokens * half) return;
+    const int t = (int)(i / half), p = (int)(i - (long long)t * half);
+    float sn, cs;
+    sincosf((float)positions[t] * freq[p], &sn, &cs);
+    table[i] = make_float2(cs, sn);
+}
+
+MM_EXPORT int mm_angle_table(const void* positions, const void* freq, void* table, int n_tokens, int half, void* stream) {
+    MM_REQUIRE(n_tokens >= 0 && half > 0, "angle table: bad sizes");
+    if (n_tokens == 0) return MM_OK;
+    mm_launch(angle_table_kernel, dim3(ceil_div((long long)n_tokens * half, 256)), dim3(256), 0, (cudaStream_t)stream,
+              (const int32_t*)positions, (const float*)freq, (float2*)table, n_tokens, half);
+    MM_CHECK_LAUNCH();
+    return MM_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// the recurrence, token by token
+// ---------------------------------------------------------------------------------------------------------------
+// q, k: fp32 rows with Gq heads of dk (row strides ldq, ldk); v: fp32 rows with H heads of dv (ldv); head h reads
+// q/k head h / (H / Gq).  gate, beta: [n, H] fp32 or null; head_decay [H] fp32 (used when gate is null).
+// out [n, H*dv] fp32.  state: the slot's S as [H, dv, dk] at `state`, slots `state_stride` floats apart.
+template <int PER, bool DELTA>
+__global__ void __launch_bounds__(128) linear_state_walk_kernel(
+    const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, int ldq, int ldk, int ldv,
+    const float* __restrict__ gate, const float* __restrict__ beta, const float* __restrict__ head_decay, float* __restrict__ out,
+    float* __restrict__ state, long long state_stride, const int32_t* __restrict__ req_meta, const int32_t* __restrict__ slots,
+    const int32_t* __restrict__ positions, int H, int Gq, int dk, int dv) {
+    constexpr int DKP = 8 * PER;
+    extern __shared__ float ls_smem[];
+    float* sq = ls_smem;                       // [AHEAD][DKP]
+    float* sk = sq + LS_AHEAD * DKP;           // [AHEAD][DKP]
+    float* sv = sk + LS_AHEAD * DKP;           // [AHEAD][COLS]
+    float* so = sv + LS_AHEAD * LS_COLS;       // [AHEAD][COLS]
+    float* sg = so + LS_AHEAD * LS_COLS;       // [AHEAD] decay
+    float* sb = sg + LS_AHEAD;                 // [AHEAD] write strength
+    float* skq = sb + LS_AHEAD;                // [AHEAD] k . q
+
+    const int h = blockIdx.y, r = blockIdx.z;
+    const int col0 = blockIdx.x * LS_COLS;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ks = lane & 7, cl = warp * 4 + (lane >> 3);
+    const int col = col0 + cl;
+    const bool col_ok = col < dv;
+    const int gq = h / (H / Gq);
+    const int t0 = req_meta ? req_meta[4 * r] : r;
+    const int n = req_meta ? req_meta[4 * r + 1] : 1;
+    float* st = state + (size_t)slots[r] * state_stride + ((size_t)h * dv + (col_ok ? col : 0)) * dk;
+    const bool fresh = positions[t0] == 0;
+    const float hd = head_decay ? head_decay[h] : 1.0f;
+
+    float S[PER];
+#pragma unroll
+    for (int e = 0; e < PER; ++e) {
+        const int i = e * 8 + ks;
+        S[e] = (col_ok && i < dk && !fresh) ? st[i] : 0.0f;
+    }
+    for (int base = 0; base < n; base += LS_AHEAD) {
+        const int cnt = min(LS_AHEAD, n - base);
+        __syncthreads();                       // the round before is read and written out
+        for (int idx = threadIdx.x; idx < cnt * DKP; idx += 128) {
+            const int tt = idx / DKP, i = idx - tt * DKP;
+            const size_t t = (size_t)(t0 + base + tt);
+            sq[idx] = i < dk ? q[t * ldq + gq * dk + i] : 0.0f;
+            sk[idx] = i < dk ? k[t * ldk + gq * dk + i] : 0.0f;
+        }
+        for (int idx = threadIdx.x; idx < cnt * LS_COLS; idx += 128) {
+            const int tt = idx / LS_COLS, c = idx - tt * LS_COLS;
+            sv[idx] = col0 + c < dv ? v[(size_t)(t0 + base + tt) * ldv + h * dv + col0 + c] : 0.0f;
+        }
+        if (threadIdx.x < cnt) {
+            const size_t t = (size_t)(t0 + base + threadIdx.x);
+            sg[threadIdx.x] = gate ? gate[t * H + h] : hd;
+            sb[threadIdx.x] = DELTA ? beta[t * H + h] : 1.0f;
+        }
+        __syncthreads();
+        for (int tt = warp; tt < cnt; tt += 4) {      // k . q of every staged token
+            float d = 0.0f;
+            for (int i = lane; i < DKP; i += 32) d = fmaf(sk[tt * DKP + i], sq[tt * DKP + i], d);
+            d = warp_sum(d);
+            if (lane == 0) skq[tt] = d;
+        }
+        __syncthreads();
+        for (int tt = 0; tt < cnt; ++tt) {
+            const float* kk = sk + tt * DKP + ks;
+            const float* qq = sq + tt * DKP + ks;
+            float dq = 0.0f, dkk = 0.0f;
+#pragma unroll
+            for (int e = 0; e < PER; ++e) {
+                dq = fmaf(S[e], qq[8 * e], dq);
+                if (DELTA) dkk = fmaf(S[e], kk[8 * e], dkk);
+            }
+#pragma unroll
+            for (int o = 1; o < 8; o <<= 1) {
+                dq += __shfl_xor_sync(0xffffffffu, dq, o);
+                if (DELTA) dkk += __shfl_xor_sync(0xffffffffu, dkk, o);
+            }
+            const float g = sg[tt];
+            const float vv = sv[tt * LS_COLS + cl];
+            const float u = DELTA ? sb[tt] * (vv - g * dkk) : vv;
+#pragma unroll
+            for (int e = 0; e < PER; ++e) S[e] = fmaf(kk[8 * e], u, g * S[e]);
+            if (ks == 0) so[tt * LS_COLS + cl] = fmaf(u, skq[tt], g * dq);     // S_new^T q = g S_old^T q + u (k . q)
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < cnt * LS_COLS; idx += 128) {
+            const int tt = idx / LS_COLS, c = idx - tt * LS_COLS;
+            if (col0 + c < dv) out[(size_t)(t0 + base + tt) * H * dv + h * dv + col0 + c] = so[idx];
+        }
+    }
+    if (col_ok) {
+#pragma unroll
+        for (int e = 0; e < PER; ++e) {
+            const int i = e * 8 + ks;
+            if (i < dk) st[i] = S[e];
+        }
+    }
+}
+
+template <int PER>
+static void ls_walk_launch(bool delta, dim3 grid, cudaStream_t s, const float* q, const float* k, const float* v, int ldq, int ldk, int ldv,
+                           const float* gate, const float* beta, const float* head_decay, float* out, float* state, long long state_stride,
+                           const int32_t* req_meta, const int32_t* slots, const int32_t* positions, int H, int Gq, int dk, int dv) {
+    const size_t smem = sizeof(float) * (LS_AHEAD * (2 * 8 * PER + 2 * LS_COLS) + 3 * LS_AHEAD);
+    if (delta)
+        mm_launch(linear_state_walk_kernel<PER, true>, grid, dim3(128), smem, s, q, k, v, ldq, ldk, ldv, gate, beta, head_decay, out, state,
+                  state_stride, req_meta, slots, positions, H, Gq, dk, dv);
+    else
+        mm_launch(linear_state_walk_kernel<PER, false>, grid, dim3(128), smem, s, q, k, v, ldq, ldk, ldv, gate, beta, head_decay, out, state,
+                  state_stride, req_meta, slots, positions, H, Gq, dk, dv);
+}
+
+MM_EXPORT int mm_linear_state_walk(const void* q, const void* k, const void* v, int ldq, int ldk, int ldv, const void* gate,
+                                   const void* beta, const void* head_decay, void* out, void* state, long long state_stride,
+                                   const void* req_meta, const void* slots, const void* positions, int n_requests, int H, int Gq,
+                                   int dk, int dv, void* stream) {
+    MM_REQUIRE(H > 0 && Gq > 0 && H % Gq == 0 && dk > 0 && dv > 0, "linear state: heads must be a positive multiple of the q/k heads");
+    MM_REQUIRE(dk <= 256, "linear state: key sizes above 256 are not supported");
+    MM_REQUIRE(gate != nullptr || head_decay != nullptr, "linear state: a decay per token or per head is needed");
+    MM_REQUIRE(state != nullptr && slots != nullptr && positions != nullptr, "linear state: the state and the positions are needed");
+    if (n_requests <= 0) return MM_OK;
+    const bool delta = beta != nullptr;
+    const dim3 grid(ceil_div(dv, LS_COLS), H, n_requests);
+    cudaStream_t s = (cudaStream_t)stream;
+#define LS_ARGS delta, grid, s, (const float*)q, (const float*)k, (const float*)v, ldq, ldk, ldv, (const float*)gate, (const float*)beta, \
+                (const float*)head_decay, (float*)out, (float*)state, state_stride, (const int32_t*)req_meta, (const int32_t*)slots,       \
+                (const int32_t*)positions, H, Gq, dk, dv
+    if (dk <= 32) ls_walk_launch<4>(LS_ARGS);
+    else if (dk <= 64) ls_walk_launch<8>(LS_ARGS);
+    else if (dk <= 96) ls_walk_launch<12>(LS_ARGS);
+    else if (dk <= 128) ls_walk_launch<16>(LS_ARGS);
+    else ls_walk_launch<32>(LS_ARGS);
+#undef LS_ARGS
+    MM_CHECK_LAUNCH();
+    return MM_OK;
+}

@@ -1,0 +1,473 @@
+// Mixture of experts: the router's choice, the rows of every expert put side by side, the experts' products over
+// those rows, and the weighted sum.
+//
+//   s = softmax(z) over all E experts (z: the router's fp32 logits);
+//   the experts stand in `groups` equal runs of neighbours; a run's score is its best expert's; only the experts of
+//   the `keep` best runs can be chosen; of those the `top` with the largest s are taken (ties: the lower index);
+//   weights: the chosen s divided by their sum (+ 1e-20);
+//   y = sum over the chosen e of weight_e * W_down[e] (act(W_gate[e] x) * (W_up[e] x)).
+//
+// Nothing here waits for the host: the lists are made on the device (route -> sort), the products run over a grid
+// that is large enough for any split of the step's rows between experts (CTAs without a tile return), and the sum
+// over a token's experts is taken in the order of its choice, so a token's output does not depend on its neighbours.
+#include "common.cuh"
+#include "mma_sync.cuh"
+
+// ---------------------------------------------------------------------------------------------------------------
+// the router's choice: one warp per token
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void warp_argmax(float& v, int& i) {      // the largest value, the lowest index among equals
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+        if (ov > v || (ov == v && oi < i)) {
+            v = ov;
+            i = oi;
+        }
+    }
+}
+
+__global__ void moe_route_kernel(const float* __restrict__ z, int ldz, int n_tokens, int E, int top, int groups, int keep,
+                                 int32_t* __restrict__ idx, float* __restrict__ wts) {
+    extern __shared__ float route_smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int t = blockIdx.x * warps + warp;
+    if (t >= n_tokens) return;
+    float* s = route_smem + (size_t)warp * (E + groups);       // scores, then the runs' scores (negative: run not kept)
+    float* gs = s + E;
+    const float* zr = z + (size_t)t * ldz;
+    float m = -INFINITY;
+    for (int e = lane; e < E; e += 32) m = fmaxf(m, zr[e]);
+    m = warp_max(m);
+    float sum = 0.0f;
+    for (int e = lane; e < E; e += 32) {
+        const float p = expf(zr[e] - m);
+        s[e] = p;
+        sum += p;
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sum;
+    for (int e = lane; e < E; e += 32) s[e] *= inv;
+    __syncwarp();
+    const int size = E / groups;
+    if (keep < groups) {
+        for (int g = lane; g < groups; g += 32) {
+            float b = 0.0f;
+            for (int e = 0; e < size; ++e) b = fmaxf(b, s[g * size + e]);
+            gs[g] = b;
+        }
+        __syncwarp();
+        // the keep best runs get their score negated and shifted below zero: what stays non-negative is dropped
+        for (int kk = 0; kk < keep; ++kk) {
+            float bv = -1.0f;
+            int bi = 0x7fffffff;
+            for (int g = lane; g < groups; g += 32)
+                if (gs[g] >= 0.0f && (gs[g] > bv)) {
+                    bv = gs[g];
+                    bi = g;
+                }
+            warp_argmax(bv, bi);
+            if (lane == 0 && bi != 0x7fffffff) gs[bi] = -1.0f;
+            __syncwarp();
+        }
+        for (int e = lane; e < E; e += 32)
+            if (gs[e / size] >= 0.0f) s[e] = -1.0f - s[e];      // not eligible; the score survives as -(1 + s)
+        __syncwarp();
+    }
+    float total = 0.0f;
+    for (int kk = 0; kk < top; ++kk) {
+        float bv = -1.0f;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32)
+            if (s[e] >= 0.0f && s[e] > bv) {
+                bv = s[e];
+                bi = e;
+            }
+        warp_argmax(bv, bi);
+        if (bi == 0x7fffffff) {     // fewer eligible experts than `top`: the rest of the choice carries no weight
+            bi = 0;
+            bv = 0.0f;
+        } else if (lane == 0) {
+            s[bi] = -3.0f;
+        }
+        __syncwarp();
+        total += bv;
+        if (lane == 0) {
+            idx[(size_t)t * top + kk] = bi;
+            wts[(size_t)t * top + kk] = bv;
+        }
+    }
+    __syncwarp();
+    if (lane == 0) {
+        const float d = total + 1e-20f;
+        for (int kk = 0; kk < top; ++kk) wts[(size_t)t * top + kk] /= d;
+    }
+}
+
+MM_EXPORT int mm_moe_route(const void* z, int ldz, int n_tokens, int E, int top, int groups, int keep, void* idx, void* wts, void* stream) {
+    MM_REQUIRE(n_tokens >= 0 && E > 0 && top > 0 && top <= E && groups > 0 && E % groups == 0 && keep > 0 && keep <= groups && ldz >= E,
+               "moe route: experts must split into equal runs, and 0 < top <= experts, 0 < keep <= runs");
+    MM_REQUIRE((size_t)(E + groups) * 4 * sizeof(float) <= 48 * 1024, "moe route: too many experts for the router's shared memory");
+    if (n_tokens == 0) return MM_OK;
+    const int warps = 4;
+    mm_launch(moe_route_kernel, dim3(ceil_div(n_tokens, warps)), dim3(warps * 32), (size_t)warps * (E + groups) * sizeof(float),
+              (cudaStream_t)stream, (const float*)z, ldz, n_tokens, E, top, groups, keep, (int32_t*)idx, (float*)wts);
+    MM_CHECK_LAUNCH();
+    return MM_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// rows by expert: offsets [E + 1] and, for every place in the sorted order, the row (token * top + choice) it holds
+// ---------------------------------------------------------------------------------------------------------------
+// One block.  Rows keep their order inside an expert (a row's place is the number of rows of its expert before it), so the
+// lists are the same on every run.
+__global__ void moe_sort_kernel(const int32_t* __restrict__ idx, int n_rows, int E, int32_t* __restrict__ offsets, int32_t* __restrict__ order) {
+    extern __shared__ int32_t sort_smem[];     // counts [E], then the running cursors [E]
+    int32_t* counts = sort_smem;
+    int32_t* cursor = counts + E;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    for (int r = threadIdx.x; r < n_rows; r += blockDim.x) atomicAdd(&counts[idx[r]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int acc = 0;
+        for (int e = 0; e < E; ++e) {
+            offsets[e] = acc;
+            cursor[e] = acc;
+            acc += counts[e];
+        }
+        offsets[E] = acc;
+    }
+    __syncthreads();
+    // stable placement: the rows are taken in rounds of blockDim.x; inside a round a row's rank among the rows of its
+    // expert is counted by ballot within the warp and by a pass over the warps in order
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    for (int base = 0; base < n_rows; base += blockDim.x) {
+        const int r = base + threadIdx.x;
+        const int e = r < n_rows ? idx[r] : -1;
+        for (int w = 0; w < warps; ++w) {           // warps take their turn: the cursor moves in row order
+            if (w == warp && e >= 0) {
+                const unsigned peers = __match_any_sync(__activemask(), e);
+                const int rank = __popc(peers & ((1u << lane) - 1));
+                const int first = __ffs(peers) - 1;
+                int start = 0;
+                if (lane == first) start = atomicAdd(&cursor[e], __popc(peers));
+                start = __shfl_sync(peers, start, first);
+                order[start + rank] = r;
+            }
+            __syncthreads();
+        }
+    }
+}
+
+MM_EXPORT int mm_moe_sort(const void* idx, int n_rows, int E, void* offsets, void* order, void* stream) {
+    MM_REQUIRE(n_rows >= 0 && E > 0 && E <= 4096, "moe sort: bad sizes");
+    mm_launch(moe_sort_kernel, dim3(1), dim3(n_rows > 256 ? 1024 : 256), (size_t)2 * E * sizeof(int32_t), (cudaStream_t)stream,
+              (const int32_t*)idx, n_rows, E, (int32_t*)offsets, (int32_t*)order);
+    MM_CHECK_LAUNCH();
+    return MM_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// the experts' products over their rows
+// ---------------------------------------------------------------------------------------------------------------
+// A CTA's tile: expert e and rows [lo, hi) of the sorted order, found from the offsets (every expert's rows start a
+// tile of their own).  Returns false when the CTA has no tile.
+template <int TM>
+__device__ __forceinline__ bool moe_tile(const int32_t* __restrict__ offsets, int E, int tile, int& e, int& lo, int& hi) {
+    int seen = 0;
+    for (int x = 0; x < E; ++x) {
+        const int a = offsets[x], b = offsets[x + 1];
+        const int tiles = (b - a + TM - 1) / TM;
+        if (tile < seen + tiles) {
+            e = x;
+            lo = a + (tile - seen) * TM;
+            hi = min(lo + TM, b);
+            return true;
+        }
+        seen += tiles;
+    }
+    return false;
+}
+
+#define MOE_BM 64
+#define MOE_BN 64
+#define MOE_BK 16
+
+// fp32 FMA units, every output summed over k in ascending order.  GATED: W is [E, 2F, K], the gate's rows then the
+// up rows, and the output is act(gate) * up over F columns, the input rows gathered through order / top; otherwise
+// W is [E, N, K], the input rows are the sorted ones and output row order[i] is written.
+template <typename TA, typename TW, typename TC, bool GATED>
+__global__ void __launch_bounds__(256) moe_gemm_simt_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, TC* __restrict__ C, int ldc,
+                                                            const int32_t* __restrict__ offsets, const int32_t* __restrict__ order, int E, int top,
+                                                            int N, int K) {
+    __shared__ float As[MOE_BK][MOE_BM + 4];
+    __shared__ float Ws[MOE_BK][MOE_BN + 4];
+    __shared__ float Us[GATED ? MOE_BK : 1][MOE_BN + 4];
+    __shared__ int32_t rows[MOE_BM];
+    __shared__ int tile_info[3];
+    const int tid = threadIdx.x;
+    if (tid == 0) {
+        int e = -1, lo = 0, hi = 0;
+        if (!moe_tile<MOE_BM>(offsets, E, blockIdx.y, e, lo, hi)) e = -1;
+        tile_info[0] = e;
+        tile_info[1] = lo;
+        tile_info[2] = hi;
+    }
+    __syncthreads();
+    const int e = tile_info[0], lo = tile_info[1], hi = tile_info[2];
+    if (e < 0) return;
+    const int M = hi - lo;
+    if (tid < MOE_BM) rows[tid] = tid < M ? (GATED ? order[lo + tid] / top : lo + tid) : 0;
+    __syncthreads();
+    const int tx = tid & 15, ty = tid >> 4;
+    const int n0 = blockIdx.x * MOE_BN;
+    const TW* We = W + (size_t)e * (GATED ? 2 : 1) * N * K;
+    float acc[4][4], up[GATED ? 4 : 1][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            acc[i][j] = 0.0f;
+            if (GATED) up[i][j] = 0.0f;
+        }
+    for (int k0 = 0; k0 < K; k0 += MOE_BK) {
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+            const int i = tid + x * 256;
+            const int r = i >> 4, kk = i & 15;
+            const int k = k0 + kk;
+            float a = 0.0f, w = 0.0f, u = 0.0f;
+            if (k < K) {
+                if (r < M) a = to_f32<TA>(A[(size_t)rows[r] * lda + k]);
+                if (n0 + r < N) {
+                    w = to_f32<TW>(We[(size_t)(n0 + r) * K + k]);
+                    if (GATED) u = to_f32<TW>(We[(size_t)(N + n0 + r) * K + k]);
+                }
+            }
+            As[kk][r] = a;
+            Ws[kk][r] = w;
+            if (GATED) Us[kk][r] = u;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < MOE_BK; ++kk) {
+            float a[4], w[4], u[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                w[j] = Ws[kk][tx * 4 + j];
+                u[j] = GATED ? Us[kk][tx * 4 + j] : 0.0f;
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+                    if (GATED) up[i][j] = fmaf(a[i], u[j], up[i][j]);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int m = ty * 4 + i;
+        if (m >= M) continue;
+        const size_t out_row = GATED ? (size_t)(lo + m) : (size_t)order[lo + m];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= N) continue;
+            float v = acc[i][j];
+            if (GATED) v = v / (1.0f + expf(-v)) * up[i][j];
+            C[out_row * ldc + n] = from_f32<TC>(v);
+        }
+    }
+}
+
+// bfloat16 on the tensor cores (mma.sync m16n8k16, fp32 accumulation): the same tiles, 64 rows x 64 columns, four
+// warps of 32 x 32 (gated: gate and up accumulators side by side), K in steps of 32 through shared memory.
+template <bool GATED, typename TC>
+__global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ W,
+                                                           TC* __restrict__ C, int ldc, const int32_t* __restrict__ offsets,
+                                                           const int32_t* __restrict__ order, int E, int top, int N, int K) {
+    constexpr int BK = 32, LD = BK + 8;      // 80-byte rows: ldmatrix reads without bank conflicts
+    __shared__ __align__(16) __nv_bfloat16 As[2][MOE_BM][LD];
+    __shared__ __align__(16) __nv_bfloat16 Ws[2][GATED ? 2 * MOE_BN : MOE_BN][LD];
+    __shared__ int32_t rows[MOE_BM];
+    __shared__ int tile_info[3];
+    const int tid = threadIdx.x;
+    if (tid == 0) {
+        int e = -1, lo = 0, hi = 0;
+        if (!moe_tile<MOE_BM>(offsets, E, blockIdx.y, e, lo, hi)) e = -1;
+        tile_info[0] = e;
+        tile_info[1] = lo;
+        tile_info[2] = hi;
+    }
+    __syncthreads();
+    const int e = tile_info[0], lo = tile_info[1], hi = tile_info[2];
+    if (e < 0) return;
+    const int M = hi - lo;
+    if (tid < MOE_BM) rows[tid] = tid < M ? (GATED ? order[lo + tid] / top : lo + tid) : -1;
+    __syncthreads();
+    const int warp = tid >> 5, lane = tid & 31;
+    const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
+    const int n0 = blockIdx.x * MOE_BN;
+    const __nv_bfloat16* We = W + (size_t)e * (GATED ? 2 : 1) * N * K;
+    constexpr int WROWS = GATED ? 2 * MOE_BN : MOE_BN;
+    float acc[2][4][4], up[GATED ? 2 : 1][4][4];
+#pragma unroll
+    for (int a = 0; a < 2; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                acc[a][b][c] = 0.0f;
+                if (GATED) up[a][b][c] = 0.0f;
+            }
+    auto load = [&](int stage, int k0) {
+        // 16-byte chunks: 4 per row of 32 k
+        for (int i = tid; i < MOE_BM * 4; i += 128) {
+            const int r = i >> 2, c = (i & 3) * 8;
+            __nv_bfloat16* dst = &As[stage][r][c];
+            if (rows[r] >= 0 && k0 + c < K) cp_async16(dst, A + (size_t)rows[r] * lda + k0 + c);
+            else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        }
+        for (int i = tid; i < WROWS * 4; i += 128) {
+            const int r = i >> 2, c = (i & 3) * 8;
+            const int n = GATED ? (r < MOE_BN ? n0 + r : N + n0 + (r - MOE_BN)) : n0 + r;
+            const bool ok = (GATED ? (r < MOE_BN ? n0 + r : n0 + r - MOE_BN) : n0 + r) < N;
+            __nv_bfloat16* dst = &Ws[stage][r][c];
+            if (ok && k0 + c < K) cp_async16(dst, We + (size_t)n * K + k0 + c);
+            else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        }
+        cp_async_commit();
+    };
+    const int steps = (K + BK - 1) / BK;
+    load(0, 0);
+    for (int s = 0; s < steps; ++s) {
+        if (s + 1 < steps) {
+            load((s + 1) & 1, (s + 1) * BK);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const int st = s & 1;
+#pragma unroll
+        for (int kk = 0; kk < BK; kk += 16) {
+            uint32_t af[2][4];
+#pragma unroll
+            for (int mi = 0; mi < 2; ++mi)
+                ldmatrix_x4(af[mi][0], af[mi][1], af[mi][2], af[mi][3], &As[st][wm + mi * 16 + (lane & 15)][kk + (lane >> 4) * 8]);
+#pragma unroll
+            for (int nj = 0; nj < 2; ++nj) {
+                uint32_t b0, b1, b2, b3;
+                // rows wn + nj*16 .. +15 of W: matrices (n 0-7, k 0-7), (n 0-7, k 8-15), (n 8-15, k 0-7), (n 8-15, k 8-15)
+                ldmatrix_x4(b0, b1, b2, b3, &Ws[st][wn + nj * 16 + (lane & 7) + ((lane >> 4) << 3)][kk + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+                for (int mi = 0; mi < 2; ++mi) {
+                    mma_bf16(acc[mi][nj * 2], af[mi], b0, b1);
+                    mma_bf16(acc[mi][nj * 2 + 1], af[mi], b2, b3);
+                }
+                if (GATED) {
+                    ldmatrix_x4(b0, b1, b2, b3, &Ws[st][MOE_BN + wn + nj * 16 + (lane & 7) + ((lane >> 4) << 3)][kk + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+                    for (int mi = 0; mi < 2; ++mi) {
+                        mma_bf16(up[mi][nj * 2], af[mi], b0, b1);
+                        mma_bf16(up[mi][nj * 2 + 1], af[mi], b2, b3);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int m = wm + mi * 16 + (lane >> 2) + half * 8;
+            if (m >= M) continue;
+            const size_t out_row = GATED ? (size_t)(lo + m) : (size_t)order[lo + m];
+#pragma unroll
+            for (int ni = 0; ni < 4; ++ni)
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const int n = n0 + wn + ni * 8 + (lane & 3) * 2 + c;
+                    if (n >= N) continue;
+                    float v = acc[mi][ni][half * 2 + c];
+                    if (GATED) v = v / (1.0f + __expf(-v)) * up[mi][ni][half * 2 + c];
+                    C[out_row * ldc + n] = from_f32<TC>(v);
+                }
+        }
+}
+
+// A [rows, lda] (gated: the step's tokens; else the sorted hidden rows), W the experts' stacked matrices, C: gated
+// [n_rows, N] in sorted order, else [n_rows, N] with row order[i] written.  n_rows = tokens * top.
+MM_EXPORT int mm_moe_gemm(const void* A, int a_dtype, int lda, const void* W, int w_dtype, void* C, int c_dtype, int ldc, const void* offsets,
+                          const void* order, int n_rows, int E, int top, int N, int K, int gated, int tensor_cores, void* stream) {
+    MM_REQUIRE(n_rows >= 0 && E > 0 && top > 0 && N > 0 && K > 0 && lda >= K && ldc >= N, "moe gemm: bad sizes");
+    if (n_rows == 0) return MM_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid(ceil_div(N, MOE_BN), ceil_div(n_rows, MOE_BM) + E);
+    typedef __nv_bfloat16 bf;
+    const int32_t* off = (const int32_t*)offsets;
+    const int32_t* ord = (const int32_t*)order;
+    if (tensor_cores && a_dtype == MM_BF16 && w_dtype == MM_BF16 && K % 8 == 0 && lda % 8 == 0 && ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0) {
+        if (gated && c_dtype == MM_BF16)
+            mm_launch(moe_gemm_mma_kernel<true, bf>, grid, dim3(128), 0, s, (const bf*)A, lda, (const bf*)W, (bf*)C, ldc, off, ord, E, top, N, K);
+        else if (!gated && c_dtype == MM_BF16)
+            mm_launch(moe_gemm_mma_kernel<false, bf>, grid, dim3(128), 0, s, (const bf*)A, lda, (const bf*)W, (bf*)C, ldc, off, ord, E, top, N, K);
+        else if (!gated && c_dtype == MM_F32)
+            mm_launch(moe_gemm_mma_kernel<false, float>, grid, dim3(128), 0, s, (const bf*)A, lda, (const bf*)W, (float*)C, ldc, off, ord, E, top, N, K);
+        else
+            MM_REQUIRE(false, "moe gemm: this combination of dtypes is not built");
+        MM_CHECK_LAUNCH();
+        return MM_OK;
+    }
+#define MOE_SIMT(TA, TW, TC)                                                                                                                  \
+    do {                                                                                                                                      \
+        if (gated)                                                                                                                            \
+            mm_launch(moe_gemm_simt_kernel<TA, TW, TC, true>, grid, dim3(256), 0, s, (const TA*)A, lda, (const TW*)W, (TC*)C, ldc, off, ord, E, top, N, K); \
+        else                                                                                                                                  \
+            mm_launch(moe_gemm_simt_kernel<TA, TW, TC, false>, grid, dim3(256), 0, s, (const TA*)A, lda, (const TW*)W, (TC*)C, ldc, off, ord, E, top, N, K); \
+    } while (0)
+    if (a_dtype == MM_F32 && w_dtype == MM_F32 && c_dtype == MM_F32) MOE_SIMT(float, float, float);
+    else if (a_dtype == MM_BF16 && w_dtype == MM_BF16 && c_dtype == MM_BF16) MOE_SIMT(bf, bf, bf);
+    else if (a_dtype == MM_BF16 && w_dtype == MM_BF16 && c_dtype == MM_F32) MOE_SIMT(bf, bf, float);
+    else MM_REQUIRE(false, "moe gemm: this combination of dtypes is not built");
+#undef MOE_SIMT
+    MM_CHECK_LAUNCH();
+    return MM_OK;
+}
+
+// out[t, :] = sum over the token's choices c, in order, of wts[t, c] * y[t * top + c, :]
+template <typename TY, typename TO>
+__global__ void moe_combine_kernel(const TY* __restrict__ y, const float* __restrict__ wts, TO* __restrict__ out, int top, int d) {
+    const size_t t = blockIdx.x;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float acc = 0.0f;
+        for (int c = 0; c < top; ++c) acc = fmaf(wts[t * top + c], to_f32<TY>(y[(t * top + c) * d + i]), acc);
+        out[t * d + i] = from_f32<TO>(acc);
+    }
+}
+
+MM_EXPORT int mm_moe_combine(const void* y, int y_dtype, const void* wts, void* out, int out_dtype, int n_tokens, int top, int d, void* stream) {
+    MM_REQUIRE(n_tokens >= 0 && top > 0 && d > 0, "moe combine: bad sizes");
+    if (n_tokens == 0) return MM_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    typedef __nv_bfloat16 bf;
+    const dim3 grid(n_tokens), block(d >= 1024 ? 256 : 128);
+    if (y_dtype == MM_F32 && out_dtype == MM_F32)
+        mm_launch(moe_combine_kernel<float, float>, grid, block, 0, s, (const float*)y, (const float*)wts, (float*)out, top, d);
+    else if (y_dtype == MM_F32 && out_dtype == MM_BF16)
+        mm_launch(moe_combine_kernel<float, bf>, grid, block, 0, s, (const float*)y, (const float*)wts, (bf*)out, top, d);
+    else if (y_dtype == MM_BF16 && out_dtype == MM_BF16)
+        mm_launch(moe_combine_kernel<bf, bf>, grid, block, 0, s, (const bf*)y, (const float*)wts, (bf*)out, top, d);
+    else
+        MM_REQUIRE(false, "moe combine: this combination of dtypes is not built");
+    MM_CHECK_LAUNCH();
+    return MM_OK;
+}

@@ -93,14 +93,14 @@ def sink_plan(ctx, n_tokens: int, tile_rows: int = SINK_TILE_ROWS):
 
 
 def paged_sink_attention(q, cache, out, ctx, num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int, window: int,
-                         scale: float, sink: bool) -> torch.Tensor:
+                         scale: float, sink: bool, sink_logit=None, dist_bias=None) -> torch.Tensor:
     """Windowed attention with a softmax sink over pools of keys ``[pages, G, page, key_dim]`` and values
     ``[pages, G, page, value_dim]``.  bfloat16 with key and value sizes the tensor-core kernels are built for: a tiled
     kernel for portions, a kernel that shares keys between the query heads of a KV head for single tokens; anything
     else: the fp32-arithmetic kernel."""
     k_pages, v_pages, table = cache.arrays["k"], cache.arrays["v"], cache.block_table
     if (USE_SINK_MMA and q.dtype == torch.bfloat16 and scale > 0 and num_heads // num_kv_heads <= 16
-            and _sink_lib().mm_attention_sink_supported(key_dim, value_dim)):
+            and sink_logit is None and dist_bias is None and _sink_lib().mm_attention_sink_supported(key_dim, value_dim)):
         from .lib import check
         lib = _sink_lib()
         # equal key and value sizes of 64 or 128: the tcgen05 prefill kernel of the plain attention, told of the sink
@@ -152,4 +152,4 @@ def paged_sink_attention(q, cache, out, ctx, num_heads: int, num_kv_heads: int, 
                   "attention_sink_decode_bf16")
         return out
     return ops.attention_sink_generic(q, k_pages, v_pages, out, ctx.positions, ctx.token_req, table, cache.page_size, num_heads,
-                                      num_kv_heads, key_dim, value_dim, window, scale, sink)
+                                      num_kv_heads, key_dim, value_dim, window, scale, sink, sink_logit=sink_logit, dist_bias=dist_bias)

@@ -59,10 +59,20 @@ _PROTOTYPES = {
     "mm_embedding_bigram": [P, P, P, P, P, P, P, P, I, P, I, I, I, I, c_longlong, c_longlong, P],
     "mm_qkv_pairs_post": [P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, F, P],
     "mm_rope_pairs_table": [P, P, P, I, I, P],
-    "mm_attention_sink_generic": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
+    "mm_attention_sink_generic": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, P, P, I, P],
     "mm_mingru_walk": [P, P, I, P, P, P, P, P, I, I, P],
     "mm_mingru_chunked": [P, P, I, P, P, P, P, P, P, P, P, I, I, I, P],
     "mm_bias_act": [P, P, I, P, I, I, I, I, P],
+    "mm_causal_conv_walk": [P, I, I, P, I, P, c_longlong, P, P, P, I, I, P],
+    "mm_linear_state_prep": [P, I, I, I, I, I, I, I, I, I, P, I, I, F, F, F, I, I, I, P, P, P, P, P],
+    "mm_angle_table": [P, P, P, I, I, P],
+    "mm_linear_state_walk": [P, P, P, I, I, I, P, P, P, P, P, c_longlong, P, P, P, I, I, I, I, I, P],
+    "mm_gated_group_norm": [P, I, I, P, I, I, P, I, P, I, I, I, I, F, I, I, P],
+    "mm_normed_mean2": [P, P, P, P, P, I, I, I, F, F, P],
+    "mm_moe_route": [P, I, I, I, I, I, I, P, P, P],
+    "mm_moe_sort": [P, I, I, P, P, P],
+    "mm_moe_gemm": [P, I, I, P, I, P, I, I, P, P, I, I, I, I, I, I, I, P],
+    "mm_moe_combine": [P, I, P, P, I, I, I, I, P],
 }
 
 

@@ -750,9 +750,12 @@ def qkv_pairs_post(qkv: torch.Tensor, q_out: torch.Tensor, k_pages: Optional[tor
 
 def attention_sink_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor, positions: torch.Tensor,
                            token_req: torch.Tensor, block_table: torch.Tensor, page_size: int, num_heads: int, num_kv_heads: int,
-                           key_dim: int, value_dim: int, window: int, scale: float, sink: bool) -> torch.Tensor:
+                           key_dim: int, value_dim: int, window: int, scale: float, sink: bool,
+                           sink_logit: Optional[torch.Tensor] = None, dist_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Windowed causal attention of every token over its request's pages with keys of ``key_dim`` and values of
-    ``value_dim``; with ``sink`` the softmax denominator has one added (fp32 arithmetic, any sizes)."""
+    ``value_dim``; with ``sink`` the softmax denominator has one added, with ``sink_logit`` (fp32 [heads]) the head's
+    ``exp(logit)``; ``dist_bias`` (fp32 [rows, heads]) is added to the scaled score by distance, its last row standing
+    for every larger distance (fp32 arithmetic, any sizes)."""
     _need(q, "attention q")
     n = q.shape[0]
     _need(out, "attention out", q.dtype)
@@ -765,10 +768,19 @@ def attention_sink_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
     _need(positions, "positions", torch.int32)
     _need(token_req, "token_req", torch.int32)
     _need(block_table, "block_table", torch.int32)
+    if sink_logit is not None:
+        _need(sink_logit, "sink logits", torch.float32)
+        if sink_logit.numel() != num_heads:
+            raise KernelError("attention: one sink logit per head")
+    if dist_bias is not None:
+        _need(dist_bias, "distance bias", torch.float32)
+        if dist_bias.dim() != 2 or dist_bias.shape[1] != num_heads or dist_bias.shape[0] < 1:
+            raise KernelError("attention: the distance bias is [rows, heads]")
     check(_lib.load().mm_attention_sink_generic(
         q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), dtype_code(q.dtype), positions.data_ptr(),
         token_req.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size, n, num_heads, num_kv_heads, key_dim,
-        value_dim, int(window), float(scale), int(bool(sink)), _stream()), "attention_sink_generic")
+        value_dim, int(window), float(scale), int(bool(sink)), _ptr(sink_logit), _ptr(dist_bias),
+        dist_bias.shape[0] - 1 if dist_bias is not None else 0, _stream()), "attention_sink_generic")
     return out
 
 
@@ -860,4 +872,194 @@ def bias_act(x: torch.Tensor, bias: Optional[torch.Tensor], activation: str, out
             raise KernelError("bias_act: bias shape mismatch")
     check(_lib.load().mm_bias_act(x.data_ptr(), _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32, out.data_ptr(),
                                   dtype_code(x.dtype), n, f, ACTIVATIONS[activation], _stream()), "bias_act")
+    return out
+
+
+# ---- mixers with a matrix state per head (csrc/linear_state.cu) -------------------------------------------------------
+def causal_conv_walk(x: torch.Tensor, channels: int, taps: torch.Tensor, tail: torch.Tensor, req_meta: Optional[torch.Tensor],
+                     slots: torch.Tensor, positions: torch.Tensor, n_requests: int, silu: bool = True) -> torch.Tensor:
+    """Short causal convolution over time on the first ``channels`` columns of ``x`` [n, ld] fp32, in place, followed by
+    silu.  ``taps`` [channels, K] fp32 (last column: the current token); ``tail`` [slots, stride] fp32 holds each request's
+    last K-1 inputs at ``[j * channels + c]`` (j = 0 the most recent) and is left updated."""
+    _need(x, "conv rows", torch.float32)
+    _need(taps, "conv taps", torch.float32)
+    _need(slots, "state slots", torch.int32)
+    _need(positions, "positions", torch.int32)
+    if tail.dtype != torch.float32 or not tail.is_cuda or tail.stride(-1) != 1:
+        raise KernelError("conv: the state is fp32 with unit stride in its last axis")
+    K = taps.shape[1]
+    if taps.shape[0] != channels or x.shape[1] < channels or tail.shape[1] < (K - 1) * channels:
+        raise KernelError("conv: shape mismatch")
+    check(_lib.load().mm_causal_conv_walk(x.data_ptr(), x.shape[1], channels, taps.data_ptr(), K, tail.data_ptr(), tail.stride(0),
+                                          _ptr(req_meta), slots.data_ptr(), positions.data_ptr(), int(n_requests), int(bool(silu)),
+                                          _stream()), "causal_conv_walk")
+    return x
+
+
+def angle_table(positions: torch.Tensor, freq: torch.Tensor) -> torch.Tensor:
+    """(cos, sin) of ``position * freq[i]`` as fp32 [n, len(freq), 2]."""
+    _need(positions, "positions", torch.int32)
+    _need(freq, "frequencies", torch.float32)
+    n, half = positions.numel(), freq.numel()
+    out = torch.empty((n, half, 2), dtype=torch.float32, device=positions.device)
+    check(_lib.load().mm_angle_table(positions.data_ptr(), freq.data_ptr(), out.data_ptr(), n, half, _stream()), "angle_table")
+    return out
+
+
+def linear_state_prep(x: torch.Tensor, q_off: int, k_off: int, v_off: int, qk_heads: int, dk: int, n_v: int, *, silu: bool = False,
+                      rot: Optional[torch.Tensor] = None, rot_dims: int = 0, unit: bool = False, unit_eps: float = 0.0,
+                      q_scale: float = 1.0, k_scale: float = 1.0, a_off: int = -1, b_off: int = -1, heads: int = 0,
+                      A_log: Optional[torch.Tensor] = None, dt_bias: Optional[torch.Tensor] = None):
+    """What stands between the projection and the recurrence, in place on the fp32 rows ``x`` [n, ld]: silu on q, k and v;
+    rotation of the half-split pairs of q and k by ``rot`` [n, rot_dims/2, 2]; unit length of every q and k head; the
+    two scales.  Returns (gate, beta), each [n, heads] fp32 or None: with ``a_off`` >= 0 the decay per token
+    ``exp(-exp(A_log) softplus(a + dt_bias))`` from the row's columns ``a_off..``, with ``b_off`` >= 0 the delta rule's write
+    strength ``sigmoid(b)`` from the columns ``b_off..``."""
+    _need(x, "projection rows", torch.float32)
+    n, ld = x.shape
+    gate = beta = None
+    if a_off >= 0:
+        _need(A_log, "A_log", torch.float32)
+        _need(dt_bias, "dt_bias", torch.float32)
+        gate = torch.empty((n, heads), dtype=torch.float32, device=x.device)
+    if b_off >= 0:
+        beta = torch.empty((n, heads), dtype=torch.float32, device=x.device)
+    if rot_dims:
+        _need(rot, "rotation table", torch.float32)
+        if rot.shape != (n, rot_dims // 2, 2):
+            raise KernelError("rotation table: wrong shape")
+    if max(q_off, k_off) + qk_heads * dk > ld or v_off + n_v > ld:
+        raise KernelError("linear state prep: columns outside the row")
+    check(_lib.load().mm_linear_state_prep(x.data_ptr(), ld, n, q_off, k_off, v_off, qk_heads, dk, n_v, int(bool(silu)),
+                                           _ptr(rot) if rot_dims else None, int(rot_dims), int(bool(unit)), float(unit_eps),
+                                           float(q_scale), float(k_scale), int(a_off), int(b_off), int(heads), _ptr(A_log), _ptr(dt_bias),
+                                           _ptr(gate), _ptr(beta), _stream()), "linear_state_prep")
+    return gate, beta
+
+
+def linear_state_walk(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, req_meta: Optional[torch.Tensor],
+                      slots: torch.Tensor, positions: torch.Tensor, n_requests: int, heads: int, qk_heads: int, dk: int, dv: int,
+                      gate: Optional[torch.Tensor] = None, beta: Optional[torch.Tensor] = None,
+                      head_decay: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Per head ``S <- g S; u = v`` (or ``beta (v - S^T k)`` when ``beta`` is given); ``S <- S + k u^T; o = S^T q`` over each
+    request's tokens in order.  q, k: fp32 column slices [n, qk_heads * dk], v [n, heads * dv] (any row stride);
+    ``gate`` [n, heads] or ``head_decay`` [heads]; ``state`` [slots, stride] fp32 holds S as [heads, dv, dk] at its start
+    and is left updated.  Returns o fp32 [n, heads * dv]."""
+    for t, what in ((q, "q"), (k, "k"), (v, "v")):
+        if t.dtype != torch.float32 or not t.is_cuda or t.stride(1) != 1:
+            raise KernelError(f"linear state {what}: fp32 rows with unit column stride are needed")
+    n = q.shape[0]
+    if q.shape[1] != qk_heads * dk or k.shape != q.shape or v.shape != (n, heads * dv):
+        raise KernelError("linear state: shape mismatch")
+    if state.dtype != torch.float32 or state.stride(-1) != 1 or state.shape[1] < heads * dv * dk:
+        raise KernelError("linear state: the state is fp32 [slots, >= heads * dv * dk]")
+    for t, what in ((gate, "gate"), (beta, "beta")):
+        if t is not None:
+            _need(t, what, torch.float32)
+            if t.shape != (n, heads):
+                raise KernelError(f"linear state {what}: wrong shape")
+    if head_decay is not None:
+        _need(head_decay, "head decay", torch.float32)
+    _need(slots, "state slots", torch.int32)
+    _need(positions, "positions", torch.int32)
+    out = torch.empty((n, heads * dv), dtype=torch.float32, device=q.device)
+    check(_lib.load().mm_linear_state_walk(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), k.stride(0), v.stride(0), _ptr(gate),
+                                           _ptr(beta), _ptr(head_decay), out.data_ptr(), state.data_ptr(), state.stride(0), _ptr(req_meta),
+                                           slots.data_ptr(), positions.data_ptr(), int(n_requests), heads, qk_heads, dk, dv, _stream()),
+          "linear_state_walk")
+    return out
+
+
+GATE_ACTIVATIONS = {"silu": 1, "sigmoid": 2}
+
+
+def gated_group_norm(x: torch.Tensor, groups: int, group_size: int, out_dtype: torch.dtype, *, eps: float = 0.0, normalize: bool = True,
+                     weight: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, activation: str = "silu") -> torch.Tensor:
+    """``x[t, g, :] / rms(x[t, g, :]) * weight * act(gate[t, g, :])`` with each factor optional; ``weight`` fp32 of
+    ``group_size`` (one for all groups) or ``groups * group_size``; x and gate may be column slices."""
+    n = x.shape[0]
+    for t, what in ((x, "x"), (gate, "gate")):
+        if t is not None and (not t.is_cuda or t.stride(1) != 1 or t.shape != (n, groups * group_size)):
+            raise KernelError(f"gated norm {what}: [n, groups * group_size] with unit column stride is needed")
+    w_stride = 0
+    if weight is not None:
+        _need(weight, "gated norm weight", torch.float32)
+        if weight.numel() not in (group_size, groups * group_size):
+            raise KernelError("gated norm: the weight has group_size or groups * group_size numbers")
+        w_stride = 0 if weight.numel() == group_size and groups > 1 else (group_size if weight.numel() == groups * group_size else 0)
+    out = torch.empty((n, groups * group_size), dtype=out_dtype, device=x.device)
+    check(_lib.load().mm_gated_group_norm(x.data_ptr(), dtype_code(x.dtype), x.stride(0), _ptr(gate), dtype_code(gate.dtype) if gate is not None else F32,
+                                          gate.stride(0) if gate is not None else 0, _ptr(weight), w_stride, out.data_ptr(), dtype_code(out_dtype),
+                                          n, groups, group_size, float(eps), int(bool(normalize)), GATE_ACTIVATIONS[activation], _stream()),
+          "gated_group_norm")
+    return out
+
+
+def normed_mean2(a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch.Tensor, eps: float, scale: float = 0.5) -> torch.Tensor:
+    """``scale * (a / rms(a) * wa + b / rms(b) * wb)`` row by row; the weights fp32."""
+    _need(a, "normed mean a")
+    _need(b, "normed mean b", a.dtype)
+    _need(wa, "normed mean weight", torch.float32)
+    _need(wb, "normed mean weight", torch.float32)
+    n, d = a.shape
+    if b.shape != a.shape or wa.numel() != d or wb.numel() != d:
+        raise KernelError("normed mean: shape mismatch")
+    out = torch.empty_like(a)
+    check(_lib.load().mm_normed_mean2(a.data_ptr(), b.data_ptr(), wa.data_ptr(), wb.data_ptr(), out.data_ptr(), dtype_code(a.dtype), n, d,
+                                      float(eps), float(scale), _stream()), "normed_mean2")
+    return out
+
+
+# ---- mixture of experts (csrc/moe.cu) -----------------------------------------------------------------------------------
+def moe_route(logits: torch.Tensor, top: int, groups: int, keep: int):
+    """The router's choice from fp32 logits [n, E]: (experts int32 [n, top], weights fp32 [n, top])."""
+    _need(logits, "router logits", torch.float32)
+    n, E = logits.shape
+    idx = torch.empty((n, top), dtype=torch.int32, device=logits.device)
+    wts = torch.empty((n, top), dtype=torch.float32, device=logits.device)
+    check(_lib.load().mm_moe_route(logits.data_ptr(), E, n, E, int(top), int(groups), int(keep), idx.data_ptr(), wts.data_ptr(), _stream()), "moe_route")
+    return idx, wts
+
+
+def moe_sort(idx: torch.Tensor, experts: int):
+    """Rows (token * top + choice) put side by side by expert: (offsets int32 [E + 1], order int32 [rows])."""
+    _need(idx, "expert choice", torch.int32)
+    rows = idx.numel()
+    offsets = torch.empty((experts + 1,), dtype=torch.int32, device=idx.device)
+    order = torch.empty((max(rows, 1),), dtype=torch.int32, device=idx.device)
+    check(_lib.load().mm_moe_sort(idx.data_ptr(), rows, int(experts), offsets.data_ptr(), order.data_ptr(), _stream()), "moe_sort")
+    return offsets, order
+
+
+def moe_gemm(a: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, order: torch.Tensor, n_rows: int, top: int, gated: bool,
+             out_dtype: torch.dtype, tensor_cores: bool = True) -> torch.Tensor:
+    """The experts' products over their rows.  ``gated``: ``a`` [tokens, K] are the step's rows, ``w`` [E, 2F, K] the gate's
+    rows then the up rows of every expert, result ``silu(gate) * up`` [n_rows, F] in sorted order.  Otherwise ``a``
+    [n_rows, K] are sorted rows, ``w`` [E, N, K], and row ``order[i]`` of the result [n_rows, N] gets sorted row i's product."""
+    _need(a, "moe rows")
+    _need(w, "moe weights", a.dtype)
+    _need(offsets, "moe offsets", torch.int32)
+    _need(order, "moe order", torch.int32)
+    E, rows_w, K = w.shape
+    N = rows_w // 2 if gated else rows_w
+    if a.shape[1] != K or (not gated and a.shape[0] != n_rows):
+        raise KernelError("moe gemm: shape mismatch")
+    out = torch.empty((n_rows, N), dtype=out_dtype, device=a.device)
+    check(_lib.load().mm_moe_gemm(a.data_ptr(), dtype_code(a.dtype), a.stride(0), w.data_ptr(), dtype_code(w.dtype), out.data_ptr(),
+                                  dtype_code(out_dtype), N, offsets.data_ptr(), order.data_ptr(), int(n_rows), E, int(top), N, K,
+                                  int(bool(gated)), int(bool(tensor_cores)), _stream()), "moe_gemm")
+    return out
+
+
+def moe_combine(y: torch.Tensor, wts: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """``out[t] = sum_c wts[t, c] * y[t * top + c]`` in the order of the choice."""
+    _need(y, "moe outputs")
+    _need(wts, "moe weights", torch.float32)
+    n, top = wts.shape
+    d = y.shape[1]
+    if y.shape[0] != n * top:
+        raise KernelError("moe combine: shape mismatch")
+    out = torch.empty((n, d), dtype=out_dtype, device=y.device)
+    check(_lib.load().mm_moe_combine(y.data_ptr(), dtype_code(y.dtype), wts.data_ptr(), out.data_ptr(), dtype_code(out_dtype), n, top, d, _stream()),
+          "moe_combine")
     return out

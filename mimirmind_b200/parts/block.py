@@ -128,6 +128,37 @@ class SandwichNormBlock(Block):
         return NormedRows(made) if made is not None else None
 
 
+@BLOCKS.register("parallel_branches")
+class ParallelBranchesBlock(Block):
+    """Mixer and feed-forward side by side, each behind a norm of its own over the same stream:
+    ``x += mixer(norm1(x)) + ffn(norm2(x))``; a layer whose feed-forward is of kind ``none`` has the first branch only.
+    The mixer's branch is added into the fp32 residual stream here, the feed-forward's is left pending so that the add
+    fuses into the norm that follows, whichever layer owns it."""
+
+    def __init__(self, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        from .mlp import NoFeedForward
+        self.has_ffn = not isinstance(self.feed_forward, NoFeedForward)
+
+    def forward(self, residual: torch.Tensor, pending, ctx: StepContext, cache: LayerCache,
+                successor: Optional[Block] = None):
+        dump = ctx.dump or (lambda stage, t: None)
+        h = self.mixer_norm.forward(residual, pending)           # the stream is complete from here on
+        dump("attn_norm", h)
+        branch = self.mixer.forward(h, ctx, cache)
+        dump("attn_out", branch)
+        if not self.has_ffn:
+            if ctx.dump is not None:
+                dump("l_out", residual + branch.to(residual.dtype))
+            return branch
+        out = self.feed_forward.forward(self.ffn_norm.forward(residual, None), ctx)
+        dump("ffn_mlp", out)
+        ops_add(residual, branch)
+        if ctx.dump is not None:
+            dump("l_out", residual + out.to(residual.dtype))
+        return out
+
+
 def ops_add(residual: torch.Tensor, delta: torch.Tensor) -> None:
     from ..kernels import ops
     ops.add_residual(residual, delta)

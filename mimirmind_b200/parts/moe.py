@@ -1,0 +1,64 @@
+"""Mixture of experts with a softmax router and a choice limited to the best runs of experts.
+
+``s = softmax(h·W_routerᵀ)`` over all ``experts`` in fp32; the experts stand in ``groups`` equal runs of neighbours, a run is
+scored by its best expert and only the ``keep`` best runs are eligible; the ``top`` eligible experts with the largest ``s``
+are chosen and weighted by ``s / (sum of the chosen s + 1e-20)``.  Expert: ``W_down (silu(W_gate h) ⊙ W_up h)``, no biases.
+The output is the weighted sum of the chosen experts' outputs.
+
+The experts' matrices are stacked at load (``[E, 2F, D]`` gate rows then up rows, ``[E, D, F]``).  A step routes on the
+device, puts the rows of every expert side by side, and runs two grouped products over them (``csrc/moe.cu``); nothing
+waits for the host, so a decode step with this feed-forward can be captured.
+"""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+
+from ..config.spec import PartSpec, TensorSpec
+from ..kernels import ops
+from ..registry import FEED_FORWARDS
+from .base import FeedForward, Runtime, StepContext, WeightView
+from .linear import linear
+
+
+@FEED_FORWARDS.register("routed_experts")
+class RoutedExperts(FeedForward):
+    """spec params: hidden, ff, experts, top, groups, keep, router (tensor name), expert (a name pattern with ``{}`` for
+    the expert's number, e.g. ``mlp.e{}``; its matrices are ``.gate``, ``.up``, ``.down``)."""
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec, prefix: str) -> List[TensorSpec]:
+        d, f = spec["hidden"], spec["ff"]
+        out = [TensorSpec(prefix + spec["router"], (spec["experts"], d), role="router")]
+        for e in range(spec["experts"]):
+            stem = prefix + spec["expert"].format(e)
+            out += [TensorSpec(stem + ".gate", (f, d)), TensorSpec(stem + ".up", (f, d)), TensorSpec(stem + ".down", (d, f))]
+        return out
+
+    def __init__(self, spec: PartSpec, weights: WeightView, rt: Runtime):
+        super().__init__(spec, weights, rt)
+        self.hidden, self.ff = int(spec["hidden"]), int(spec["ff"])
+        self.experts, self.top = int(spec["experts"]), int(spec["top"])
+        self.groups, self.keep = int(spec.get("groups", 1)), int(spec.get("keep", 1))
+        if self.experts % self.groups or not (0 < self.keep <= self.groups) or not (0 < self.top <= self.keep * (self.experts // self.groups)):
+            raise ValueError("routed experts: the experts split into equal runs, 0 < keep <= runs, and top fits into the kept runs")
+        self.w_router = weights.take(spec["router"]).float().contiguous()        # the router runs in fp32
+        stacked_in, stacked_out = [], []
+        for e in range(self.experts):
+            stem = spec["expert"].format(e)
+            stacked_in.append(torch.cat([weights.take(stem + ".gate"), weights.take(stem + ".up")], dim=0))
+            stacked_out.append(weights.take(stem + ".down"))
+        self.w_in = torch.stack(stacked_in).to(rt.dtype).contiguous()       # [E, 2F, D]
+        self.w_out = torch.stack(stacked_out).to(rt.dtype).contiguous()     # [E, D, F]
+        del stacked_in, stacked_out
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        n = x.shape[0]
+        z = linear(x, self.w_router, None, self.rt, out_dtype=torch.float32)
+        idx, wts = ops.moe_route(z, self.top, self.groups, self.keep)
+        offsets, order = ops.moe_sort(idx, self.experts)
+        tc = self.rt.matmul != "simt"
+        hidden = ops.moe_gemm(x, self.w_in, offsets, order, n * self.top, self.top, True, self.rt.dtype, tensor_cores=tc)
+        y = ops.moe_gemm(hidden, self.w_out, offsets, order, n * self.top, self.top, False, torch.float32, tensor_cores=tc)
+        return ops.moe_combine(y, wts, self.rt.dtype)

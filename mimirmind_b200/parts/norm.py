@@ -19,23 +19,27 @@ from .base import NativeDesc, Norm, Runtime, WeightView
 
 @NORMS.register("rmsnorm")
 class RMSNorm(Norm):
-    """spec params: width, eps, weight (tensor name under the prefix)."""
+    """spec params: width, eps, weight (tensor name under the prefix), offset (default 0: the stored weight multiplies
+    directly; 1: the weight is stored around zero and ``1 + w`` multiplies, formed once at load in fp32)."""
 
     @classmethod
     def tensor_specs(cls, spec: PartSpec, prefix: str) -> List[TensorSpec]:
-        return [TensorSpec(prefix + spec["weight"], (spec["width"],), role="norm")]
+        return [TensorSpec(prefix + spec["weight"], (spec["width"],), role="norm0" if float(spec.get("offset", 0.0)) else "norm")]
 
     def __init__(self, spec: PartSpec, weights: WeightView, rt: Runtime):
         super().__init__(spec, weights, rt)
         self.width = int(spec["width"])
         self.eps = float(spec["eps"])
+        self.offset = float(spec.get("offset", 0.0))
         self.weight = weights.get(spec["weight"]).contiguous()
+        if self.offset:
+            self.weight = (self.weight.float() + self.offset).contiguous()
 
     def factors(self):
         return self.weight, self.eps
 
     def native(self):
-        if type(self) is not RMSNorm:
+        if type(self) is not RMSNorm or self.offset:
             return None
         return NativeDesc("rmsnorm", {"width": self.width, "eps": self.eps}, {"weight": self.weight})
 

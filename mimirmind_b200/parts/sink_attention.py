@@ -9,11 +9,20 @@ Value mixing (``v_mix``): the first layer of a model that names a mixing key is 
 that key caches and uses ``(1 − λ)·v + λ·v_source`` of the same token, λ a scalar tensor of the layer.  The source's
 values of the step's tokens are handed on through the step context, so nothing of it is cached twice.
 
+Three further options, each a parameter.  A *learned sink*: ``sink`` names a tensor with one logit per head, and the
+denominator holds ``exp(logit_h)`` instead of 1.  A *distance bias*: ``distance_bias = {"table", "far", "rows"}`` names a
+tensor ``[rows, heads]`` (``rows`` absent: as many as the checkpoint's table has) that is added, unscaled, to the scaled score of a key ``n`` tokens back, at row ``n`` for
+``n < rows/2`` and beyond that at rows spaced evenly in ``ln n`` up to ``far``:
+``min(rows − 1, rows/2 + floor(ln(n / (rows/2)) / ln(far / (rows/2)) · (rows − rows/2)))``; it is unrolled at load into a
+table by distance whose last row stands for every larger distance.  An *output gate*: ``gate`` names a projection, and the
+joined heads are multiplied by ``sigmoid(h·W_gᵀ)`` before the output projection.
+
 Every size and constant is a parameter; the pools are per-token arrays ``k`` ``(G, key_dim)`` and ``v``
 ``(G, value_dim)`` of the paged cache.
 """
 from __future__ import annotations
 
+import math
 from typing import List, Optional
 
 import torch
@@ -25,11 +34,27 @@ from .base import CacheArray, KVCacheSpec, LayerCache, Mixer, Runtime, StepConte
 from .linear import linear
 
 
+def distance_rows(rows: int, far: float) -> List[int]:
+    """Row of the bias table for every distance 0 .. ceil(far): one row per distance below ``rows // 2``, then rows
+    spaced evenly in the logarithm of the distance up to ``far``; the last entry (distance >= far) is the last row."""
+    half = rows // 2
+    if half < 1 or far <= half:
+        raise ValueError(f"distance bias: {rows} rows need far > {half}, got {far}")
+    out = []
+    for n in range(int(math.ceil(far)) + 1):
+        if n < half:
+            out.append(n)
+        else:
+            out.append(min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half)))))
+    return out
+
+
 @MIXERS.register("sink_attention")
 class SinkAttention(Mixer):
-    """spec params: hidden, num_heads, num_kv_heads, key_dim, value_dim, window (0: all), scale, sink (bool), bias
-    (bool: q, k, v and o), position (PartSpec or None), v_mix (None, "source" or "mix"), v_mix_key, and the tensor
-    names q, k, v, o (weights; biases are the name + ``bias_suffix``) and mix (the scalar λ)."""
+    """spec params: hidden, num_heads, num_kv_heads, key_dim, value_dim, window (0: all), scale, sink (bool, or the
+    name of a tensor of learned logits), bias (bool: q, k, v and o), position (PartSpec or None), v_mix (None, "source"
+    or "mix"), v_mix_key, distance_bias (None or {"table", "far", "rows"}), gate (None or a tensor name), and the
+    tensor names q, k, v, o (weights; biases are the name + ``bias_suffix``) and mix (the scalar λ)."""
 
     @classmethod
     def tensor_specs(cls, spec: PartSpec, prefix: str) -> List[TensorSpec]:
@@ -42,6 +67,13 @@ class SinkAttention(Mixer):
                     TensorSpec(prefix + spec["v"] + sfx, (G * dv,), role="bias"), TensorSpec(prefix + spec["o"] + sfx, (d,), role="bias")]
         if spec.get("v_mix"):
             out.append(TensorSpec(prefix + spec["mix"], (), role="mix"))
+        if isinstance(spec.get("sink"), str):
+            out.append(TensorSpec(prefix + spec["sink"], (H,), role="bias"))
+        if spec.get("distance_bias"):
+            # rows None: the checkpoint's table decides how many rows there are
+            out.append(TensorSpec(prefix + spec["distance_bias"]["table"], (spec["distance_bias"].get("rows") or -1, H), role="bias"))
+        if spec.get("gate"):
+            out.append(TensorSpec(prefix + spec["gate"], (H * dv, d)))
         return out
 
     def __init__(self, spec: PartSpec, weights: WeightView, rt: Runtime):
@@ -51,7 +83,16 @@ class SinkAttention(Mixer):
         self.key_dim, self.value_dim = int(spec["key_dim"]), int(spec["value_dim"])
         self.window = int(spec.get("window", 0) or 0)
         self.scale = float(spec["scale"])
-        self.sink = bool(spec.get("sink", True))
+        sink = spec.get("sink", True)
+        self.sink = bool(sink)
+        self.sink_logit = weights.take(sink).float().contiguous() if isinstance(sink, str) else None
+        self.dist_bias = None
+        db = spec.get("distance_bias")
+        if db:
+            table = weights.take(db["table"]).float()
+            rows = torch.tensor(distance_rows(int(table.shape[0]), float(db["far"])), dtype=torch.long, device=table.device)
+            self.dist_bias = table[rows].contiguous()            # [ceil(far) + 1, heads] by distance
+        self.w_gate = weights.take(spec["gate"]).contiguous() if spec.get("gate") else None
         if self.num_heads % self.num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         pos_spec: Optional[PartSpec] = spec.get("position")
@@ -117,5 +158,9 @@ class SinkAttention(Mixer):
         ops.qkv_pairs_post(qkv, q, k_pages, v_pages, v_first, rot, slots, cache.page_size, H, G, dk, dv, self.rot_dims, mode, self.mix)
         out = torch.empty((n, H * dv), dtype=self.rt.dtype, device=qkv.device)
         from ..kernels import attention as attn_kernels
-        attn_kernels.paged_sink_attention(q, cache, out, ctx, H, G, dk, dv, self.window, self.scale, self.sink)
+        attn_kernels.paged_sink_attention(q, cache, out, ctx, H, G, dk, dv, self.window, self.scale, self.sink,
+                                          sink_logit=self.sink_logit, dist_bias=self.dist_bias)
+        if self.w_gate is not None:
+            gate = linear(x, self.w_gate, None, self.rt)
+            out = ops.gated_group_norm(out, 1, H * dv, self.rt.dtype, normalize=False, gate=gate, activation="sigmoid")
         return linear(out, self.w_o, self.b_o, self.rt)

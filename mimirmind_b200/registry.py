@@ -117,4 +117,4 @@ def _ensure_builtin() -> None:
         return
     _builtin_loaded = True
     from . import parts  # noqa: F401  (registers part kinds)
-    from .models import bigerax, qwen2  # noqa: F401  (register the architectures)
+    from .models import bigerax, domelix, qwen2  # noqa: F401  (register the architectures)

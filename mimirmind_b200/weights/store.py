@@ -124,11 +124,19 @@ def random_tensors(spec: ModelSpec, seed: int, dtype: torch.dtype, device="cpu")
     for name, ts in expected_tensors(spec).items():
         if ts.optional:
             continue
+        if any(int(x) < 0 for x in ts.shape):
+            raise WeightsError(f"tensor '{name}' has an extent that only a checkpoint gives; the configuration must name it for random weights")
         gen = torch.Generator(device=device)
         gen.manual_seed(_tensor_seed(seed, name))
         x = torch.randn(ts.shape, generator=gen, device=device, dtype=torch.float32)
         if ts.role == "norm":
             x = 1.0 + NORM_STD * x
+        elif ts.role == "norm0":          # a norm weight stored around zero
+            x = NORM_STD * x
+        elif ts.role == "taps":           # a short convolution: a few taps per channel
+            x = 0.5 * x
+        elif ts.role == "router":         # spread enough that the choice of experts is not a near tie
+            x = 0.2 * x
         elif ts.role == "bias":
             x = BIAS_STD * x
         elif ts.role == "mix":
