@@ -6,7 +6,8 @@
 //
 // The sink is a key of score 0 that has no value: it only takes its share of the weights.  The fp32-arithmetic
 // kernel also takes a learned sink, exp(logit of the head) in its place, and a learned bias per (distance, head)
-// that is added to the scaled score: bias[min(a - j, rows - 1)][h] (a table by distance, clamped at its last row).
+// that is added to the scaled score: bias[h][min(a - j, rows - 1)] (a table by distance per head, clamped at its last
+// entry); the bfloat16 tensor-core kernels (attention_sink_mma.cu) take both as well.
 //
 // This file holds (1) the step between the q/k/v projection and attention: rotation of adjacent pairs
 // (2i, 2i+1) of q and k by position (angles from a per-step table), the mixing of this layer's values with those of
@@ -222,7 +223,7 @@ __global__ void attention_sink_generic_kernel(const T* __restrict__ q, const T* 
             float dot = 0.0f;
             for (int d = 0; d < dk; ++d) dot = fmaf(qs[d], to_f32<T>(kr[d]), dot);
             // a learned bias per (distance, head), not scaled: the table's last row stands for every larger distance
-            s = dist_bias ? dot + dist_bias[(size_t)min(pos - j, dist_max) * H + h] : dot;
+            s = dist_bias ? dot + dist_bias[(size_t)h * (dist_max + 1) + min(pos - j, dist_max)] : dot;
         }
         const float m_new = fmaxf(m, warp_max(s));
         const float alpha = expf(m - m_new);  // m = -inf on the first chunk gives 0

@@ -59,12 +59,14 @@ __device__ __forceinline__ void load_kv_tile2(__nv_bfloat16* dK, __nv_bfloat16* 
 // prefill
 //   tiles: int32 [n_tiles, 4] = (request index, first token row, rows in the tile, position of the first row)
 // ---------------------------------------------------------------------------
+#define SINK_LOG2E_F 1.4426950408889634f
+
 template <int DK, int DV>
 __global__ void __launch_bounds__(SATT_THREADS) attention_sink_prefill_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
     const __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ out, const int32_t* __restrict__ tiles,
     const int32_t* __restrict__ block_table, int table_width, int page_size, int H, int G, int window, float scale_log2,
-    int sink) {
+    int sink, const float* __restrict__ sink_logit, const float* __restrict__ dist_bias, int dist_max) {
     constexpr int KS = DK + 8, VS = DV + 8;
     constexpr int KSTEPS = DK / 16;
     constexpr int NT_O = DV / 8;
@@ -112,9 +114,14 @@ __global__ void __launch_bounds__(SATT_THREADS) attention_sink_prefill_kernel(
     float o[NT_O][4];
 #pragma unroll
     for (int j = 0; j < NT_O; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
-    // the sink: maximum 0 (raw score), mass 1 held by the first thread of the quad that shares a row
-    const float l0 = (sink && (lane & 3) == 0) ? 1.0f : 0.0f;
-    float m_lo = sink ? 0.0f : -INFINITY, m_hi = m_lo, l_lo = l0, l_hi = l0;
+    // the sink: maximum 0 (raw score), mass 1 held by the first thread of the quad that shares a row.  With a learned
+    // sink or a distance bias the scores are brought to their final form (scaled, bias added, in units of log2 e) right
+    // after the product, and from there on the scale is 1; the learned sink then starts the maximum at its logit.
+    const bool ext = sink_logit != nullptr || dist_bias != nullptr;
+    const float sl2 = ext ? 1.0f : scale_log2;
+    const float* bias_h = dist_bias ? dist_bias + (size_t)h * (dist_max + 1) : nullptr;
+    const float l0 = ((sink || sink_logit) && (lane & 3) == 0) ? 1.0f : 0.0f;
+    float m_lo = sink_logit ? sink_logit[h] * SINK_LOG2E_F : (sink ? 0.0f : -INFINITY), m_hi = m_lo, l_lo = l0, l_hi = l0;
 
     for (int kt = kt_begin; kt < kt_end; ++kt) {
         const int buf = (kt - kt_begin) & 1;
@@ -152,6 +159,24 @@ __global__ void __launch_bounds__(SATT_THREADS) attention_sink_prefill_kernel(
             const bool interior = (key0 + SKT - 1 <= pos0 + warp * 16) && (warp * 16 + 15 < n_rows) &&
                                   (window == 0 || key0 >= pos0 + warp * 16 + 16 - window);
             float mx_lo = m_lo, mx_hi = m_hi;
+            if (ext) {
+                // every key of the tile at least dist_max behind every row of the warp: one bias for all
+                const bool all_far = bias_h != nullptr && pos0 + warp * 16 - (key0 + SKT - 1) >= dist_max;
+                const float far_bias = bias_h ? bias_h[dist_max] * SINK_LOG2E_F : 0.0f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        float b = far_bias;
+                        if (bias_h != nullptr && !all_far) {
+                            const int key = key0 + j * 8 + (lane & 3) * 2 + (e & 1);
+                            const int dist = (e >= 2 ? pos_hi : pos_lo) - key;
+                            b = bias_h[min(max(dist, 0), dist_max)] * SINK_LOG2E_F;
+                        }
+                        s[j][e] = fmaf(s[j][e], scale_log2, b);
+                    }
+                }
+            }
             if (!interior) {
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
@@ -173,17 +198,17 @@ __global__ void __launch_bounds__(SATT_THREADS) attention_sink_prefill_kernel(
             mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
             mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
             mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-            const float use_lo = (mx_lo == -INFINITY) ? 0.0f : mx_lo * scale_log2;
-            const float use_hi = (mx_hi == -INFINITY) ? 0.0f : mx_hi * scale_log2;
-            const float a_lo = exp2f(m_lo * scale_log2 - use_lo), a_hi = exp2f(m_hi * scale_log2 - use_hi);
+            const float use_lo = (mx_lo == -INFINITY) ? 0.0f : mx_lo * sl2;
+            const float use_hi = (mx_hi == -INFINITY) ? 0.0f : mx_hi * sl2;
+            const float a_lo = exp2f(m_lo * sl2 - use_lo), a_hi = exp2f(m_hi * sl2 - use_hi);
             m_lo = mx_lo;
             m_hi = mx_hi;
             float sum_lo = 0.0f, sum_hi = 0.0f;
             uint32_t pf[4][4];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                const float p0 = exp2f(fmaf(s[j][0], scale_log2, -use_lo)), p1 = exp2f(fmaf(s[j][1], scale_log2, -use_lo));
-                const float p2 = exp2f(fmaf(s[j][2], scale_log2, -use_hi)), p3 = exp2f(fmaf(s[j][3], scale_log2, -use_hi));
+                const float p0 = exp2f(fmaf(s[j][0], sl2, -use_lo)), p1 = exp2f(fmaf(s[j][1], sl2, -use_lo));
+                const float p2 = exp2f(fmaf(s[j][2], sl2, -use_hi)), p3 = exp2f(fmaf(s[j][3], sl2, -use_hi));
                 sum_lo += p0 + p1;
                 sum_hi += p2 + p3;
                 pf[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p0, p1);
@@ -234,7 +259,8 @@ __global__ void __launch_bounds__(SATT_THREADS) attention_sink_decode_kernel(
     const __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
     float* __restrict__ part_ml, const int32_t* __restrict__ items,
     const int32_t* __restrict__ positions, const int32_t* __restrict__ token_req, const int32_t* __restrict__ block_table,
-    int table_width, int page_size, int H, int G, int window, float scale_log2, int sink) {
+    int table_width, int page_size, int H, int G, int window, float scale_log2, int sink, const float* __restrict__ sink_logit,
+    const float* __restrict__ dist_bias, int dist_max) {
     constexpr int KS = DK + 8, VS = DV + 8;
     constexpr int KSTEPS = DK / 16;
     constexpr int NT_O = DV / 8;
@@ -317,7 +343,13 @@ __global__ void __launch_bounds__(SATT_THREADS) attention_sink_decode_kernel(
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int key = key0 + j * 8 + (lane & 3) * 2 + (e & 1);
-                    const float v = (key >= k_begin && key < k_end) ? s[j][e] * scale_log2 : -INFINITY;
+                    float v = -INFINITY;
+                    if (key >= k_begin && key < k_end) {
+                        v = s[j][e] * scale_log2;
+                        // rows of the tile are the query heads of this kv head: the bias of (distance, head)
+                        const int hq = g * qpg + (lane >> 2) + (e >= 2 ? 8 : 0);
+                        if (dist_bias != nullptr && hq < H) v += dist_bias[(size_t)hq * (dist_max + 1) + min(pos - key, dist_max)] * SINK_LOG2E_F;
+                    }
                     s[j][e] = v;
                     if (e >= 2) mx_hi = fmaxf(mx_hi, v); else mx_lo = fmaxf(mx_lo, v);
                 }
@@ -388,11 +420,13 @@ __global__ void __launch_bounds__(SATT_THREADS) attention_sink_decode_kernel(
     const bool single = n_splits == 1;
     for (int idx = threadIdx.x; idx < qpg * DV; idx += SATT_THREADS) {
         const int r = idx / DV, col = idx - r * DV;
-        float m = (sink && single) ? 0.0f : -INFINITY;
+        const bool with_sink = (sink || sink_logit) && single;
+        const float sink_m = sink_logit ? sink_logit[g * qpg + r] * SINK_LOG2E_F : 0.0f;
+        float m = with_sink ? sink_m : -INFINITY;
 #pragma unroll
         for (int w = 0; w < 4; ++w) m = fmaxf(m, mml[(w * 16 + r) * 2]);
         const float mu = (m == -INFINITY) ? 0.0f : m;
-        float l = (sink && single) ? exp2f(-mu) : 0.0f, acc = 0.0f;
+        float l = with_sink ? exp2f(sink_m - mu) : 0.0f, acc = 0.0f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
             const float f = exp2f(mml[(w * 16 + r) * 2] - mu);
@@ -416,14 +450,16 @@ __global__ void __launch_bounds__(SATT_THREADS) attention_sink_decode_kernel(
 // The splits of every (item, head) put together in split order, with the sink's share: one block per (item, head).
 __global__ void attention_sink_merge_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o,
                                             const float* __restrict__ part_ml, const int32_t* __restrict__ items, int H, int dv,
-                                            int n_splits, int sink) {
+                                            int n_splits, int sink, const float* __restrict__ sink_logit) {
     const int item = blockIdx.x, h = blockIdx.y;
     const int t = items ? items[item] : item;
     const size_t p0 = ((size_t)item * H + h) * n_splits;
-    float m = sink ? 0.0f : -INFINITY;
+    const bool with_sink = sink || sink_logit;
+    const float sink_m = sink_logit ? sink_logit[h] * SINK_LOG2E_F : 0.0f;
+    float m = with_sink ? sink_m : -INFINITY;
     for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_ml[(p0 + s) * 2]);
     const float mu = (m == -INFINITY) ? 0.0f : m;
-    float l = sink ? exp2f(-mu) : 0.0f;
+    float l = with_sink ? exp2f(sink_m - mu) : 0.0f;
     for (int s = 0; s < n_splits; ++s) l += part_ml[(p0 + s) * 2 + 1] * exp2f(part_ml[(p0 + s) * 2] - mu);
     const float inv = l > 0.0f ? 1.0f / l : 0.0f;
     for (int col = threadIdx.x; col < dv; col += blockDim.x) {
@@ -438,6 +474,7 @@ static const float SINK_LOG2E = 1.4426950408889634f;
 template <int DK, int DV>
 static int launch_sink_prefill(const void* q, const void* k, const void* v, void* out, const void* tiles, int n_tiles,
                                const void* table, int table_width, int page_size, int H, int G, int window, float scale, int sink,
+                               const void* sink_logit, const void* dist_bias, int dist_max,
                                cudaStream_t s) {
     const size_t smem = (size_t)(3 * 64 * (DK + 8) + 2 * 64 * (DV + 8)) * sizeof(__nv_bfloat16);
     auto kernel = attention_sink_prefill_kernel<DK, DV>;
@@ -448,7 +485,7 @@ static int launch_sink_prefill(const void* q, const void* k, const void* v, void
     }
     mm_launch(kernel, dim3(H, n_tiles), dim3(SATT_THREADS), smem, s, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k,
               (const __nv_bfloat16*)v, (__nv_bfloat16*)out, (const int32_t*)tiles, (const int32_t*)table, table_width, page_size, H, G,
-              window, scale * SINK_LOG2E, sink);
+              window, scale * SINK_LOG2E, sink, (const float*)sink_logit, (const float*)dist_bias, dist_max);
     MM_CHECK_LAUNCH();
     return MM_OK;
 }
@@ -457,7 +494,8 @@ template <int DK, int DV>
 static int launch_sink_decode(const void* q, const void* k, const void* v, void* out, void* part_o, void* part_ml, int n_splits,
                               const void* items, int n_items,
                               const void* positions, const void* token_req, const void* table, int table_width, int page_size,
-                              int H, int G, int window, float scale, int sink, cudaStream_t s) {
+                              int H, int G, int window, float scale, int sink, const void* sink_logit, const void* dist_bias, int dist_max,
+                              cudaStream_t s) {
     const size_t kv = (size_t)SDEC_STAGES * 64 * (DK + 8 + DV + 8) * sizeof(__nv_bfloat16);
     const size_t merge = (size_t)(4 * 16 * DV + 4 * 16 * 2) * sizeof(float);
     const size_t smem = kv > merge ? kv : merge;
@@ -470,11 +508,11 @@ static int launch_sink_decode(const void* q, const void* k, const void* v, void*
     mm_launch(kernel, dim3(n_items, G, n_splits), dim3(SATT_THREADS), smem, s, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k,
               (const __nv_bfloat16*)v, (__nv_bfloat16*)out, (float*)part_o, (float*)part_ml, (const int32_t*)items,
               (const int32_t*)positions, (const int32_t*)token_req, (const int32_t*)table, table_width, page_size, H, G, window,
-              scale * SINK_LOG2E, sink);
+              scale * SINK_LOG2E, sink, (const float*)sink_logit, (const float*)dist_bias, dist_max);
     MM_CHECK_LAUNCH();
     if (n_splits > 1) {
         mm_launch(attention_sink_merge_kernel, dim3(n_items, H), dim3(DV >= 64 ? 64 : 32), 0, s, (__nv_bfloat16*)out, (const float*)part_o,
-                  (const float*)part_ml, (const int32_t*)items, H, DV, n_splits, sink);
+                  (const float*)part_ml, (const int32_t*)items, H, DV, n_splits, sink, (const float*)sink_logit);
         MM_CHECK_LAUNCH();
     }
     return MM_OK;
@@ -508,13 +546,14 @@ MM_EXPORT int mm_attention_sink_supported(int dk, int dv) {
 
 MM_EXPORT int mm_attention_sink_prefill_bf16(const void* q, const void* k_pages, const void* v_pages, void* out, const void* tiles,
                                              int n_tiles, const void* block_table, int table_width, int page_size, int H, int G,
-                                             int dk, int dv, int window, float scale, int sink, void* stream) {
+                                             int dk, int dv, int window, float scale, int sink, const void* sink_logit, const void* dist_bias,
+                                             int dist_max, void* stream) {
     MM_REQUIRE(n_tiles >= 0 && H > 0 && G > 0 && H % G == 0, "sink attention: heads must be a positive multiple of kv heads");
     MM_REQUIRE(page_size > 0 && table_width > 0 && window >= 0 && scale > 0.0f, "sink attention: bad page geometry, window or scale");
     if (n_tiles == 0) return MM_OK;
     cudaStream_t s = (cudaStream_t)stream;
     SINK_DISPATCH(launch_sink_prefill, q, k_pages, v_pages, out, tiles, n_tiles, block_table, table_width, page_size, H, G, window, scale,
-                  sink, s);
+                  sink, sink_logit, dist_bias, dist_max, s);
     mm_set_last_error("sink attention: key and value sizes must each be one of 32, 64, 96, 128");
     return MM_ERR_UNSUPPORTED;
 }
@@ -525,7 +564,7 @@ MM_EXPORT int mm_attention_sink_decode_bf16(const void* q, const void* k_pages, 
                                             void* part_ml, int n_splits, const void* items,
                                             int n_items, const void* positions, const void* token_req, const void* block_table,
                                             int table_width, int page_size, int H, int G, int dk, int dv, int window, float scale,
-                                            int sink, void* stream) {
+                                            int sink, const void* sink_logit, const void* dist_bias, int dist_max, void* stream) {
     MM_REQUIRE(n_splits >= 1 && n_splits <= 64 && (n_splits == 1 || (part_o != nullptr && part_ml != nullptr)),
                "sink attention: 1..64 splits, with scratch for more than one");
     MM_REQUIRE(n_items >= 0 && H > 0 && G > 0 && H % G == 0 && H / G <= 16, "sink attention: at most 16 query heads per kv head");
@@ -533,7 +572,7 @@ MM_EXPORT int mm_attention_sink_decode_bf16(const void* q, const void* k_pages, 
     if (n_items == 0) return MM_OK;
     cudaStream_t s = (cudaStream_t)stream;
     SINK_DISPATCH(launch_sink_decode, q, k_pages, v_pages, out, part_o, part_ml, n_splits, items, n_items, positions, token_req, block_table,
-                  table_width, page_size, H, G, window, scale, sink, s);
+                  table_width, page_size, H, G, window, scale, sink, sink_logit, dist_bias, dist_max, s);
     mm_set_last_error("sink attention: key and value sizes must each be one of 32, 64, 96, 128");
     return MM_ERR_UNSUPPORTED;
 }

@@ -64,7 +64,7 @@ __global__ void causal_conv_walk_kernel(float* __restrict__ x, int ld, int C, co
 MM_EXPORT int mm_causal_conv_walk(void* x, int ld, int C, const void* taps, int K, void* tail, long long tail_stride,
                                   const void* req_meta, const void* slots, const void* positions, int n_requests, int act, void* stream) {
     MM_REQUIRE(C > 0 && ld >= C && K >= 1 && K <= LS_MAX_TAPS, "causal conv: 1 to 8 taps, and at least as many columns as channels");
-    MM_REQUIRE(tail != nullptr && slots != nullptr && positions != nullptr, "causal conv: the state and the positions are needed");
+    MM_REQUIRE((tail != nullptr || K == 1) && slots != nullptr && positions != nullptr, "causal conv: the state and the positions are needed");
     if (n_requests <= 0) return MM_OK;
     mm_launch(causal_conv_walk_kernel, dim3(ceil_div(C, 128), n_requests), dim3(128), 0, (cudaStream_t)stream, (float*)x, ld, C,
               (const float*)taps, K, (float*)tail, tail_stride, (const int32_t*)req_meta, (const int32_t*)slots, (const int32_t*)positions, act);

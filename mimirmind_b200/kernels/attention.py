@@ -38,8 +38,8 @@ def _sink_lib():
     if not _sink_declared:
         P, I, F = c_void_p, c_int, c_float
         _lib.declare("mm_attention_sink_supported", [I, I])
-        _lib.declare("mm_attention_sink_prefill_bf16", [P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, P])
-        _lib.declare("mm_attention_sink_decode_bf16", [P, P, P, P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P])
+        _lib.declare("mm_attention_sink_prefill_bf16", [P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, P, P, I, P])
+        _lib.declare("mm_attention_sink_decode_bf16", [P, P, P, P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, P, I, P])
         _lib.declare("mm_attention_decode_tma_bf16_sink", [P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, P])
         _lib.declare("mm_attention_prefill_tcgen05_sink", [P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, F, I, P, P])
         _sink_declared = True
@@ -100,12 +100,18 @@ def paged_sink_attention(q, cache, out, ctx, num_heads: int, num_kv_heads: int, 
     else: the fp32-arithmetic kernel."""
     k_pages, v_pages, table = cache.arrays["k"], cache.arrays["v"], cache.block_table
     if (USE_SINK_MMA and q.dtype == torch.bfloat16 and scale > 0 and num_heads // num_kv_heads <= 16
-            and sink_logit is None and dist_bias is None and _sink_lib().mm_attention_sink_supported(key_dim, value_dim)):
+            and _sink_lib().mm_attention_sink_supported(key_dim, value_dim)):
         from .lib import check
         lib = _sink_lib()
         # equal key and value sizes of 64 or 128: the tcgen05 prefill kernel of the plain attention, told of the sink
         from . import attention_bf16
-        tensor_memory = (USE_SINK_TCGEN05 and key_dim == value_dim and attention_bf16.tcgen05_prefill_usable(key_dim, cache.page_size))
+        # a learned sink or a distance bias: the mma.sync kernels take them, the tcgen05 and TMA kernels do not
+        extended = sink_logit is not None or dist_bias is not None
+        sink_ptr = sink_logit.data_ptr() if sink_logit is not None else None
+        bias_ptr = dist_bias.data_ptr() if dist_bias is not None else None
+        dist_max = dist_bias.shape[1] - 1 if dist_bias is not None else 0
+        tensor_memory = (USE_SINK_TCGEN05 and not extended and key_dim == value_dim
+                         and attention_bf16.tcgen05_prefill_usable(key_dim, cache.page_size))
         tiles, n_tiles, items, n_items = sink_plan(ctx, q.shape[0], attention_bf16.TILE_ROWS_TC if tensor_memory else SINK_TILE_ROWS)
         stream = ops._stream()
         if n_tiles and tensor_memory:
@@ -117,10 +123,11 @@ def paged_sink_attention(q, cache, out, ctx, num_heads: int, num_kv_heads: int, 
         elif n_tiles:
             check(lib.mm_attention_sink_prefill_bf16(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), tiles.data_ptr(),
                                                      n_tiles, table.data_ptr(), table.shape[1], cache.page_size, num_heads, num_kv_heads,
-                                                     key_dim, value_dim, int(window), float(scale), int(bool(sink)), stream),
+                                                     key_dim, value_dim, int(window), float(scale), int(bool(sink)), sink_ptr, bias_ptr, dist_max,
+                                                     stream),
                   "attention_sink_prefill_bf16")
         tma = None
-        if n_items and USE_SINK_TMA_DECODE and key_dim == value_dim and key_dim in (64, 128) and cache.page_size in (8, 16, 32, 64):
+        if n_items and USE_SINK_TMA_DECODE and not extended and key_dim == value_dim and key_dim in (64, 128) and cache.page_size in (8, 16, 32, 64):
             # equal key and value sizes of 64 or 128: the TMA decode kernel of the plain attention, in the forms that
             # finish a row inside the kernel (one split, or the splits of a token as one cluster)
             keys = min(window, ctx.max_kv_len) if window > 0 else ctx.max_kv_len
@@ -148,7 +155,8 @@ def paged_sink_attention(q, cache, out, ctx, num_heads: int, num_kv_heads: int, 
                                                     part_ml.data_ptr() if part_ml is not None else None, splits,
                                                     items.data_ptr() if items is not None else None, n_items, ctx.positions.data_ptr(),
                                                     ctx.token_req.data_ptr(), table.data_ptr(), table.shape[1], cache.page_size, num_heads,
-                                                    num_kv_heads, key_dim, value_dim, int(window), float(scale), int(bool(sink)), stream),
+                                                    num_kv_heads, key_dim, value_dim, int(window), float(scale), int(bool(sink)), sink_ptr, bias_ptr,
+                                                    dist_max, stream),
                   "attention_sink_decode_bf16")
         return out
     return ops.attention_sink_generic(q, k_pages, v_pages, out, ctx.positions, ctx.token_req, table, cache.page_size, num_heads,

@@ -754,8 +754,8 @@ def attention_sink_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
                            sink_logit: Optional[torch.Tensor] = None, dist_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Windowed causal attention of every token over its request's pages with keys of ``key_dim`` and values of
     ``value_dim``; with ``sink`` the softmax denominator has one added, with ``sink_logit`` (fp32 [heads]) the head's
-    ``exp(logit)``; ``dist_bias`` (fp32 [rows, heads]) is added to the scaled score by distance, its last row standing
-    for every larger distance (fp32 arithmetic, any sizes)."""
+    ``exp(logit)``; ``dist_bias`` (fp32 [heads, distances]) is added to the scaled score by distance, a head's last entry
+    standing for every larger distance (fp32 arithmetic, any sizes)."""
     _need(q, "attention q")
     n = q.shape[0]
     _need(out, "attention out", q.dtype)
@@ -774,13 +774,13 @@ def attention_sink_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
             raise KernelError("attention: one sink logit per head")
     if dist_bias is not None:
         _need(dist_bias, "distance bias", torch.float32)
-        if dist_bias.dim() != 2 or dist_bias.shape[1] != num_heads or dist_bias.shape[0] < 1:
-            raise KernelError("attention: the distance bias is [rows, heads]")
+        if dist_bias.dim() != 2 or dist_bias.shape[0] != num_heads or dist_bias.shape[1] < 1:
+            raise KernelError("attention: the distance bias is [heads, distances]")
     check(_lib.load().mm_attention_sink_generic(
         q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), dtype_code(q.dtype), positions.data_ptr(),
         token_req.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size, n, num_heads, num_kv_heads, key_dim,
         value_dim, int(window), float(scale), int(bool(sink)), _ptr(sink_logit), _ptr(dist_bias),
-        dist_bias.shape[0] - 1 if dist_bias is not None else 0, _stream()), "attention_sink_generic")
+        dist_bias.shape[1] - 1 if dist_bias is not None else 0, _stream()), "attention_sink_generic")
     return out
 
 

@@ -91,7 +91,7 @@ class SinkAttention(Mixer):
         if db:
             table = weights.take(db["table"]).float()
             rows = torch.tensor(distance_rows(int(table.shape[0]), float(db["far"])), dtype=torch.long, device=table.device)
-            self.dist_bias = table[rows].contiguous()            # [ceil(far) + 1, heads] by distance
+            self.dist_bias = table[rows].t().contiguous()        # [heads, ceil(far) + 1]: a head's bias by distance
         self.w_gate = weights.take(spec["gate"]).contiguous() if spec.get("gate") else None
         if self.num_heads % self.num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")

@@ -76,13 +76,11 @@ def distance_bucket(n: int, rows: int, far: float) -> int:
     return min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half))))
 
 
-def biased_sink_attention(h, wq, wk, wv, wg, wo, rel, sink, heads, kv_heads, dim, vdim, scale, far):
-    """Causal softmax attention over all earlier tokens with grouped heads, a learned bias per (distance row, head) added to
-    the scaled score, a learned sink logit per head in the denominator only, and a sigmoid gate on the joined heads."""
-    T = h.shape[0]
-    q = (h @ wq.T).reshape(T, heads, dim)
-    k = (h @ wk.T).reshape(T, kv_heads, dim)
-    v = (h @ wv.T).reshape(T, kv_heads, vdim)
+def biased_sink_attention_core(q, k, v, rel, sink, scale, far, positions=None):
+    """q [T, H, dk], k [T, G, dk], v [T, G, dv]: causal softmax over all earlier tokens with a bias per (distance row, head)
+    added to the scaled score and exp(sink_h) in the denominator only.  Returns [T, H, dv]."""
+    T, heads, _ = q.shape
+    kv_heads, vdim = k.shape[1], v.shape[2]
     rows = rel.shape[0]
     out = np.zeros((T, heads, vdim))
     per = heads // kv_heads
@@ -93,6 +91,16 @@ def biased_sink_attention(h, wq, wk, wv, wg, wo, rel, sink, heads, kv_heads, dim
             m = max(s.max(), sink[hd])
             e = np.exp(s - m)
             out[i, hd] = (e / (e.sum() + math.exp(sink[hd] - m))) @ v[: i + 1, g]
+    return out
+
+
+def biased_sink_attention(h, wq, wk, wv, wg, wo, rel, sink, heads, kv_heads, dim, vdim, scale, far):
+    """Grouped heads, no rotation, a learned distance bias, a learned sink, and a sigmoid gate on the joined heads."""
+    T = h.shape[0]
+    q = (h @ wq.T).reshape(T, heads, dim)
+    k = (h @ wk.T).reshape(T, kv_heads, dim)
+    v = (h @ wv.T).reshape(T, kv_heads, vdim)
+    out = biased_sink_attention_core(q, k, v, rel, sink, scale, far)
     joined = out.reshape(T, heads * vdim) * sigmoid(h @ wg.T)
     return joined @ wo.T
 
@@ -220,7 +228,8 @@ def route(z, top: int, groups: int, keep: int):
 
 def mixture_of_experts(h, w: Dict[str, np.ndarray], mlp: dict):
     r = mlp["router"]
-    idx, wts = route(h @ w["router"].T, r["top"], r["groups"]["count"], r["groups"]["keep"])
+    groups = r.get("groups") or {"count": 1, "keep": 1}
+    idx, wts = route(h @ w["router"].T, r["top"], groups["count"], groups["keep"])
     out = np.zeros_like(h)
     for t in range(h.shape[0]):
         for e, a in zip(idx[t], wts[t]):
