@@ -166,7 +166,7 @@ def run_workload(name: str, layers: int) -> int:
     return 0 if verified else 1
 
 
-# ---- another design beside the closest existing one, at equal size (--compare bigerax) ---------------------------------------
+# ---- another design beside the closest existing one, at equal size (--compare bigerax | domelix) ---------------------------------------
 # Layer sizes that resemble a real model's; both models get the same width, heads, key size, window, layer count and
 # vocabulary, and feed-forwards of equal parameter count (two matrices of ff against three of 2/3 ff).
 COMPARE_SIZES = {
@@ -185,6 +185,22 @@ def bigerax_config(z):
             "embedding": {"bigram": {"buckets": 65521, "mul_prev": 33, "mul_cur": 7}}, "layers": layers}
 
 
+def domelix_config(z):
+    """Layers of the three kinds in turn (delta, parallel, retention, parallel), every layer with routed experts whose active
+    parameters equal the dense feed-forward's of the same size: 16 experts of three matrices, 4 chosen from the 2 best of 4 groups."""
+    d, H, G, dk, dv = z["width"], z["heads"], z["kv_heads"], z["dim"], z["vdim"]
+    expert_ff = -(-(2 * z["ff"] // 12) // 64) * 64
+    mlp = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": 16, "top": 4, "groups": {"count": 4, "keep": 2}}}
+    decay = [1.0 - 2.0 ** (-3 - 5 * h / max(1, H - 1)) for h in range(H)]
+    par = {"type": "parallel", "mlp": mlp,
+           "mixer": {"left": {"heads": H, "kv_heads": G, "dim": dk, "vdim": dv, "scale": dk ** -0.5, "bias_max": z["window"], "bias_rows": 32},
+                     "right": {"heads": H, "dim": dk, "vdim": dv, "decay": decay}}}
+    delta = {"type": "delta", "mlp": mlp, "mixer": {"heads": H, "kv_heads": G, "dim": dk, "vdim": dk, "conv": 4}}
+    ret = {"type": "retention", "mlp": mlp, "mixer": {"heads": H, "dim": dk, "vdim": dk, "decay": decay, "rot": {"dims": dk, "base": 10000.0}}}
+    layers = [(delta, par, ret, par)[i % 4] for i in range(z["layers"])]
+    return {"architecture": "Domelix", "vocab": z["vocab"], "width": d, "norm": {"eps": 1e-6}, "layers": layers}
+
+
 def qwen2_config(z, context):
     inter = -(-(2 * z["ff"] // 3) // 64) * 64
     return dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=z["layers"], hidden_size=z["width"],
@@ -194,8 +210,9 @@ def qwen2_config(z, context):
 
 
 def run_compare(args) -> int:
-    """Prefill and decode throughput of the Bigerax design beside the Qwen2 decoder at equal size (random weights, bfloat16):
-    one prompt in one step (median of five), and the captured decode step at the given batch over prompts of that length."""
+    """Prefill and decode throughput of one design beside the closest other one at equal size (random weights, bfloat16):
+    Bigerax beside the Qwen2 decoder, Domelix beside Bigerax; one prompt in one step (median of five), and the captured
+    decode step at the given batch over prompts of that length."""
     import numpy as np
     import torch
     from mimirmind_b200.engine.decode_graph import decode_session
@@ -210,7 +227,9 @@ def run_compare(args) -> int:
     prompt_len = args.prompt_len or PROMPT_LEN
     steps, warmup, batch = max(1, min(args.steps, 128)), max(3, args.warmup), max(1, args.batch)
     context = -(-(prompt_len + SETTLE_STEPS + warmup + steps + 1) // 1024) * 1024
-    out = {"compare": "bigerax", "beside": "qwen2", "dtype": "bf16", "data": "synthetic", "prompt_len": prompt_len, "batch": batch,
+    first, second = ("bigerax", "qwen2") if args.compare == "bigerax" else ("domelix", "bigerax")
+    configs = {"bigerax": lambda z: bigerax_config(z), "qwen2": lambda z: qwen2_config(z, context), "domelix": lambda z: domelix_config(z)}
+    out = {"compare": first, "beside": second, "dtype": "bf16", "data": "synthetic", "prompt_len": prompt_len, "batch": batch,
            "steps": steps, "warmup": warmup, "sizes": {}}
     sizes = [args.size] if args.size else sorted(COMPARE_SIZES)
     for name in sizes:
@@ -218,7 +237,7 @@ def run_compare(args) -> int:
         if args.layers:
             z["layers"] = args.layers
         row = {}
-        for which, cfg_json in (("bigerax", bigerax_config(z)), ("qwen2", qwen2_config(z, context))):
+        for which, cfg_json in ((first, configs[first](z)), (second, configs[second](z))):
             arch = get_architecture(architecture_name(cfg_json))
             spec = arch.build_spec(arch.parse_config(cfg_json, "bench"))
             model = random_model(spec, seed=0, dtype="bfloat16")
@@ -272,8 +291,8 @@ def run_compare(args) -> int:
                 runner.release(r)
             del sess, engine, runner, model
             torch.cuda.empty_cache()
-        row["prefill_ratio"] = row["bigerax"]["prefill_tokens_per_s"] / row["qwen2"]["prefill_tokens_per_s"]
-        row["decode_ratio"] = row["bigerax"]["decode_tokens_per_s"] / row["qwen2"]["decode_tokens_per_s"]
+        row["prefill_ratio"] = row[first]["prefill_tokens_per_s"] / row[second]["prefill_tokens_per_s"]
+        row["decode_ratio"] = row[first]["decode_tokens_per_s"] / row[second]["decode_tokens_per_s"]
         row["shape"] = z
         out["sizes"][name] = row
     print(json.dumps(out))
@@ -329,9 +348,9 @@ def main() -> int:
                     help="with --only decode or prefill: prompts of this many tokens instead of 2,048 (the context grows with them)")
     ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE",
                     help="set a tunable of the library's dispatch (csrc/exec/exec.h, Options) for this run, e.g. cluster_max_wanted=64")
-    ap.add_argument("--compare", default="", choices=["", "bigerax"],
-                    help="instead of the default run: prefill and decode throughput of that design beside the Qwen2 decoder at equal "
-                         "size, at layer sizes that resemble a real model's (random weights; --size, --layers, --batch, --prompt-len, --steps)")
+    ap.add_argument("--compare", default="", choices=["", "bigerax", "domelix"],
+                    help="instead of the default run: prefill and decode throughput of that design beside the closest other one (bigerax "
+                         "beside the Qwen2 decoder, domelix beside bigerax) at equal size, at layer sizes that resemble a real model's (random weights; --size, --layers, --batch, --prompt-len, --steps)")
     ap.add_argument("--size", default="", choices=[""] + sorted(COMPARE_SIZES), help="with --compare: one size only")
     args = ap.parse_args()
 

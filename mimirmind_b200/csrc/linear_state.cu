@@ -11,8 +11,7 @@
 // q, k and v between their projection and the recurrence (activation, rotation of half-split pairs, unit length,
 // scale, and the decay per token and the write strength of the delta rule), all in fp32 and in place, and (3) the recurrence as a
 // walk over each request's tokens.  Columns of S are independent of one another: a thread owns an eighth of one
-// column (its entries i = 8e + lane%8), eight lanes add up the two dot products of a token, and a block of 128
-// threads walks 16 columns of one head.  The layout of the state in a slot is [H, dv, dk]: what a warp reads is one run.
+// column, eight lanes add up the dot products of a token, and a block of 128 threads walks 16 columns of one head.  The layout of the state in a slot is [H, dv, dk]: what a warp reads is one run.
 #include "common.cuh"
 
 #define LS_MAX_TAPS 8
@@ -72,6 +71,69 @@ MM_EXPORT int mm_causal_conv_walk(void* x, int ld, int C, const void* taps, int 
     return MM_OK;
 }
 
+// The same convolution for long portions, one thread per (token, channel): y (another buffer, [n, ldy]) gets the
+// result, x stays as it is, and the state is read only; a second launch then leaves the request's last K-1 inputs in
+// the state (one thread per (request, channel), which reads what it needs of the old state before it writes).
+__global__ void causal_conv_tokens_kernel(const float* __restrict__ x, int ld, int C, const float* __restrict__ taps, int K,
+                                          const float* __restrict__ tail, long long tail_stride, float* __restrict__ y, int ldy,
+                                          const int32_t* __restrict__ token_req, const int32_t* __restrict__ req_meta,
+                                          const int32_t* __restrict__ slots, const int32_t* __restrict__ positions, int act, int n_tokens) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)n_tokens * C) return;
+    const int t = (int)(idx / C), c = (int)(idx - (long long)t * C);
+    const int r = token_req[t];
+    const int o = t - (req_meta ? req_meta[4 * r] : t);       // the token's place in its portion
+    const int pos = positions[t];
+    const float* tl = tail + (size_t)slots[r] * tail_stride;
+    float acc = 0.0f;
+    for (int j = 0; j < K; ++j) {
+        if (pos - j < 0) break;                                // before the sequence's start: zeros
+        const float in = (o - j >= 0) ? x[(size_t)(t - j) * ld + c] : tl[(size_t)(j - o - 1) * C + c];
+        acc = fmaf(taps[(size_t)c * K + (K - 1 - j)], in, acc);
+    }
+    y[(size_t)t * ldy + c] = act ? ls_silu(acc) : acc;
+}
+
+__global__ void causal_conv_tail_kernel(const float* __restrict__ x, int ld, int C, int K, float* __restrict__ tail, long long tail_stride,
+                                        const int32_t* __restrict__ req_meta, const int32_t* __restrict__ slots,
+                                        const int32_t* __restrict__ positions) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int r = blockIdx.y;
+    if (c >= C) return;
+    const int t0 = req_meta ? req_meta[4 * r] : r;
+    const int n = req_meta ? req_meta[4 * r + 1] : 1;
+    float* tl = tail + (size_t)slots[r] * tail_stride;
+    const bool fresh = positions[t0] == 0;
+    float keep[LS_MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < LS_MAX_TAPS; ++j) {
+        keep[j] = 0.0f;
+        if (j < K - 1) keep[j] = j < n ? x[(size_t)(t0 + n - 1 - j) * ld + c] : (fresh ? 0.0f : tl[(size_t)(j - n) * C + c]);
+    }
+#pragma unroll
+    for (int j = 0; j < LS_MAX_TAPS; ++j)
+        if (j < K - 1) tl[(size_t)j * C + c] = keep[j];
+}
+
+MM_EXPORT int mm_causal_conv_tokens(const void* x, int ld, int C, const void* taps, int K, void* tail, long long tail_stride, void* y, int ldy,
+                                    const void* token_req, const void* req_meta, const void* slots, const void* positions, int n_tokens,
+                                    int n_requests, int act, void* stream) {
+    MM_REQUIRE(C > 0 && ld >= C && ldy >= C && K >= 1 && K <= LS_MAX_TAPS, "causal conv: 1 to 8 taps, and at least as many columns as channels");
+    MM_REQUIRE((tail != nullptr || K == 1) && slots != nullptr && positions != nullptr && token_req != nullptr && y != nullptr && y != x,
+               "causal conv: the state, the positions, the tokens' requests and a result buffer of its own are needed");
+    if (n_tokens <= 0 || n_requests <= 0) return MM_OK;
+    mm_launch(causal_conv_tokens_kernel, dim3(ceil_div((long long)n_tokens * C, 256)), dim3(256), 0, (cudaStream_t)stream, (const float*)x, ld, C,
+              (const float*)taps, K, (const float*)tail, tail_stride, (float*)y, ldy, (const int32_t*)token_req, (const int32_t*)req_meta,
+              (const int32_t*)slots, (const int32_t*)positions, act, n_tokens);
+    MM_CHECK_LAUNCH();
+    if (K > 1) {
+        mm_launch(causal_conv_tail_kernel, dim3(ceil_div(C, 128), n_requests), dim3(128), 0, (cudaStream_t)stream, (const float*)x, ld, C, K,
+                  (float*)tail, tail_stride, (const int32_t*)req_meta, (const int32_t*)slots, (const int32_t*)positions);
+        MM_CHECK_LAUNCH();
+    }
+    return MM_OK;
+}
+
 // ---------------------------------------------------------------------------------------------------------------
 // between projection and recurrence, in place on the fp32 rows of the projection
 // ---------------------------------------------------------------------------------------------------------------
@@ -80,13 +142,15 @@ MM_EXPORT int mm_causal_conv_walk(void* x, int ld, int C, const void* taps, int 
 // of rot[t] (cos, sin per pair; made from the positions once per step); unit length (x / sqrt(sum x^2 + unit_eps))
 // when `unit`; q *= q_scale, k *= k_scale.  With a_off >= 0 also a decay per token and head,
 // gate = exp(-exp(A_log) softplus(a + dt_bias)), and with b_off >= 0 the delta rule's write strength, beta = sigmoid(b),
-// from the columns a_off.. and b_off.. of the row.
+// from the columns a_off.. and b_off.. of the row of gx (row stride gld; null: of x itself).
 __global__ void linear_state_prep_kernel(float* __restrict__ x, int ld, int q_off, int k_off, int v_off, int Gq, int dk, int n_v,
                                          int act, const float2* __restrict__ rot, int rot_dims, int unit, float unit_eps,
-                                         float q_scale, float k_scale, int a_off, int b_off, int H, const float* __restrict__ A_log,
-                                         const float* __restrict__ dt_bias, float* __restrict__ gate, float* __restrict__ beta) {
+                                         float q_scale, float k_scale, const float* __restrict__ gx, int gld, int a_off, int b_off, int H,
+                                         const float* __restrict__ A_log, const float* __restrict__ dt_bias, float* __restrict__ gate,
+                                         float* __restrict__ beta) {
     const int t = blockIdx.x;
     float* row = x + (size_t)t * ld;
+    const float* grow = gx + (size_t)t * gld;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     const int half = rot_dims / 2;
     for (int vec = warp; vec < 2 * Gq; vec += warps) {
@@ -117,14 +181,19 @@ __global__ void linear_state_prep_kernel(float* __restrict__ x, int ld, int q_of
     if (act)
         for (int d = threadIdx.x; d < n_v; d += blockDim.x) row[v_off + d] = ls_silu(row[v_off + d]);
     for (int h = threadIdx.x; h < H; h += blockDim.x) {
-        if (a_off >= 0) gate[(size_t)t * H + h] = expf(-expf(A_log[h]) * ls_softplus(row[a_off + h] + dt_bias[h]));
-        if (b_off >= 0) beta[(size_t)t * H + h] = ls_sigmoid(row[b_off + h]);
+        if (a_off >= 0) gate[(size_t)t * H + h] = expf(-expf(A_log[h]) * ls_softplus(grow[a_off + h] + dt_bias[h]));
+        if (b_off >= 0) beta[(size_t)t * H + h] = ls_sigmoid(grow[b_off + h]);
     }
 }
 
 MM_EXPORT int mm_linear_state_prep(void* x, int ld, int n_tokens, int q_off, int k_off, int v_off, int Gq, int dk, int n_v, int act,
-                                   const void* rot, int rot_dims, int unit, float unit_eps, float q_scale, float k_scale, int a_off,
-                                   int b_off, int H, const void* A_log, const void* dt_bias, void* gate, void* beta, void* stream) {
+                                   const void* rot, int rot_dims, int unit, float unit_eps, float q_scale, float k_scale, const void* gx,
+                                   int gld, int a_off, int b_off, int H, const void* A_log, const void* dt_bias, void* gate, void* beta,
+                                   void* stream) {
+    if (gx == nullptr) {
+        gx = x;
+        gld = ld;
+    }
     MM_REQUIRE(n_tokens >= 0 && Gq > 0 && dk > 0 && n_v >= 0 && ld > 0, "linear state prep: bad sizes");
     MM_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dk && (rot_dims == 0 || rot != nullptr), "linear state prep: the rotated dimensions must be even, at most the head size, and have their table");
     MM_REQUIRE(a_off < 0 || (H > 0 && A_log && dt_bias && gate), "linear state prep: the decay per token needs its inputs and its output");
@@ -132,7 +201,8 @@ MM_EXPORT int mm_linear_state_prep(void* x, int ld, int n_tokens, int q_off, int
     if (a_off < 0 && b_off < 0) H = 0;
     if (n_tokens == 0) return MM_OK;
     mm_launch(linear_state_prep_kernel, dim3(n_tokens), dim3(128), 0, (cudaStream_t)stream, (float*)x, ld, q_off, k_off, v_off, Gq, dk, n_v, act,
-              (const float2*)rot, rot_dims, unit, unit_eps, q_scale, k_scale, a_off, b_off, H, (const float*)A_log, (const float*)dt_bias,
+              (const float2*)rot, rot_dims, unit, unit_eps, q_scale, k_scale, (const float*)gx, gld, a_off, b_off, H, (const float*)A_log,
+              (const float*)dt_bias,
               (float*)gate, (float*)beta);
     MM_CHECK_LAUNCH();
     return MM_OK;
@@ -164,21 +234,34 @@ MM_EXPORT int mm_angle_table(const void* positions, const void* freq, void* tabl
 // q, k: fp32 rows with Gq heads of dk (row strides ldq, ldk); v: fp32 rows with H heads of dv (ldv); head h reads
 // q/k head h / (H / Gq).  gate, beta: [n, H] fp32 or null; head_decay [H] fp32 (used when gate is null).
 // out [n, H*dv] fp32.  state: the slot's S as [H, dv, dk] at `state`, slots `state_stride` floats apart.
+//
+// A thread's entries of its column are i = 32 (e / 4) + 4 (lane % 8) + e % 4, e < PER: the eight lanes of a column
+// read q and k of a token as 16-byte words without bank conflicts.  The tokens of a request come in rounds of
+// LS_AHEAD through two shared-memory buffers filled by asynchronous copies, so a round's loads run under the round
+// before it; within a round nothing but the eight-lane sums synchronises, and the loop over tokens is unrolled so
+// that the sums of neighbouring tokens overlap (without the delta rule only S itself is carried from token to token).
+__device__ __forceinline__ void ls_cp_async4(void* smem, const void* gmem) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(gmem));
+}
+__device__ __forceinline__ void ls_cp_async16(void* smem, const void* gmem) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(gmem));
+}
+__device__ __forceinline__ void ls_cp_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void ls_cp_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
 template <int PER, bool DELTA>
 __global__ void __launch_bounds__(128) linear_state_walk_kernel(
     const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, int ldq, int ldk, int ldv,
     const float* __restrict__ gate, const float* __restrict__ beta, const float* __restrict__ head_decay, float* __restrict__ out,
     float* __restrict__ state, long long state_stride, const int32_t* __restrict__ req_meta, const int32_t* __restrict__ slots,
-    const int32_t* __restrict__ positions, int H, int Gq, int dk, int dv) {
+    const int32_t* __restrict__ positions, int H, int Gq, int dk, int dv, int vec_ok) {
     constexpr int DKP = 8 * PER;
-    extern __shared__ float ls_smem[];
-    float* sq = ls_smem;                       // [AHEAD][DKP]
-    float* sk = sq + LS_AHEAD * DKP;           // [AHEAD][DKP]
-    float* sv = sk + LS_AHEAD * DKP;           // [AHEAD][COLS]
-    float* so = sv + LS_AHEAD * LS_COLS;       // [AHEAD][COLS]
-    float* sg = so + LS_AHEAD * LS_COLS;       // [AHEAD] decay
-    float* sb = sg + LS_AHEAD;                 // [AHEAD] write strength
-    float* skq = sb + LS_AHEAD;                // [AHEAD] k . q
+    constexpr int ROUND = LS_AHEAD * (2 * DKP + LS_COLS + 2);      // floats of one buffer: q, k, v, decay, write strength
+    extern __shared__ __align__(16) float ls_smem[];
+    float* so = ls_smem + 2 * ROUND;                               // [AHEAD][COLS]
 
     const int h = blockIdx.y, r = blockIdx.z;
     const int col0 = blockIdx.x * LS_COLS;
@@ -196,55 +279,104 @@ __global__ void __launch_bounds__(128) linear_state_walk_kernel(
     float S[PER];
 #pragma unroll
     for (int e = 0; e < PER; ++e) {
-        const int i = e * 8 + ks;
+        const int i = (e >> 2) * 32 + ks * 4 + (e & 3);
         S[e] = (col_ok && i < dk && !fresh) ? st[i] : 0.0f;
     }
-    for (int base = 0; base < n; base += LS_AHEAD) {
+    // what no copy writes (entries beyond dk, columns beyond dv) stays zero in both buffers
+    for (int i = threadIdx.x; i < 2 * ROUND; i += 128) ls_smem[i] = 0.0f;
+    __syncthreads();
+
+    auto fill = [&](int buf, int base) {
+        float* sq = ls_smem + buf * ROUND;
+        float* sk = sq + LS_AHEAD * DKP;
+        float* sv = sk + LS_AHEAD * DKP;
+        float* sg = sv + LS_AHEAD * LS_COLS;
+        float* sb = sg + LS_AHEAD;
         const int cnt = min(LS_AHEAD, n - base);
-        __syncthreads();                       // the round before is read and written out
-        for (int idx = threadIdx.x; idx < cnt * DKP; idx += 128) {
-            const int tt = idx / DKP, i = idx - tt * DKP;
-            const size_t t = (size_t)(t0 + base + tt);
-            sq[idx] = i < dk ? q[t * ldq + gq * dk + i] : 0.0f;
-            sk[idx] = i < dk ? k[t * ldk + gq * dk + i] : 0.0f;
-        }
-        for (int idx = threadIdx.x; idx < cnt * LS_COLS; idx += 128) {
-            const int tt = idx / LS_COLS, c = idx - tt * LS_COLS;
-            sv[idx] = col0 + c < dv ? v[(size_t)(t0 + base + tt) * ldv + h * dv + col0 + c] : 0.0f;
+        if (vec_ok) {
+            const int per_row = dk >> 2;
+            for (int idx = threadIdx.x; idx < cnt * per_row; idx += 128) {
+                const int tt = idx / per_row, i = (idx - tt * per_row) * 4;
+                const size_t t = (size_t)(t0 + base + tt);
+                ls_cp_async16(sq + tt * DKP + i, q + t * ldq + gq * dk + i);
+                ls_cp_async16(sk + tt * DKP + i, k + t * ldk + gq * dk + i);
+            }
+            const int vcols = min(LS_COLS, dv - col0) >> 2;
+            for (int idx = threadIdx.x; idx < cnt * vcols; idx += 128) {
+                const int tt = idx / vcols, c = (idx - tt * vcols) * 4;
+                ls_cp_async16(sv + tt * LS_COLS + c, v + (size_t)(t0 + base + tt) * ldv + h * dv + col0 + c);
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < cnt * dk; idx += 128) {
+                const int tt = idx / dk, i = idx - tt * dk;
+                const size_t t = (size_t)(t0 + base + tt);
+                ls_cp_async4(sq + tt * DKP + i, q + t * ldq + gq * dk + i);
+                ls_cp_async4(sk + tt * DKP + i, k + t * ldk + gq * dk + i);
+            }
+            const int vcols = min(LS_COLS, dv - col0);
+            for (int idx = threadIdx.x; idx < cnt * vcols; idx += 128) {
+                const int tt = idx / vcols, c = idx - tt * vcols;
+                ls_cp_async4(sv + tt * LS_COLS + c, v + (size_t)(t0 + base + tt) * ldv + h * dv + col0 + c);
+            }
         }
         if (threadIdx.x < cnt) {
             const size_t t = (size_t)(t0 + base + threadIdx.x);
-            sg[threadIdx.x] = gate ? gate[t * H + h] : hd;
-            sb[threadIdx.x] = DELTA ? beta[t * H + h] : 1.0f;
+            if (gate) ls_cp_async4(sg + threadIdx.x, gate + t * H + h);
+            else sg[threadIdx.x] = hd;
+            if (DELTA) ls_cp_async4(sb + threadIdx.x, beta + t * H + h);
+        }
+        ls_cp_commit();
+    };
+
+    fill(0, 0);
+    int buf = 0;
+    for (int base = 0; base < n; base += LS_AHEAD, buf ^= 1) {
+        const int cnt = min(LS_AHEAD, n - base);
+        if (base + LS_AHEAD < n) {
+            fill(buf ^ 1, base + LS_AHEAD);
+            ls_cp_wait<1>();
+        } else {
+            ls_cp_wait<0>();
         }
         __syncthreads();
-        for (int tt = warp; tt < cnt; tt += 4) {      // k . q of every staged token
-            float d = 0.0f;
-            for (int i = lane; i < DKP; i += 32) d = fmaf(sk[tt * DKP + i], sq[tt * DKP + i], d);
-            d = warp_sum(d);
-            if (lane == 0) skq[tt] = d;
-        }
-        __syncthreads();
+        const float* sq = ls_smem + buf * ROUND;
+        const float* sk = sq + LS_AHEAD * DKP;
+        const float* sv = sk + LS_AHEAD * DKP;
+        const float* sg = sv + LS_AHEAD * LS_COLS;
+        const float* sb = sg + LS_AHEAD;
+#pragma unroll 4
         for (int tt = 0; tt < cnt; ++tt) {
-            const float* kk = sk + tt * DKP + ks;
-            const float* qq = sq + tt * DKP + ks;
-            float dq = 0.0f, dkk = 0.0f;
+            const float4* q4 = reinterpret_cast<const float4*>(sq + tt * DKP) + ks;
+            const float4* k4 = reinterpret_cast<const float4*>(sk + tt * DKP) + ks;
+            float kk[PER];
+            float dq[4] = {0.0f, 0.0f, 0.0f, 0.0f}, dkk[4] = {0.0f, 0.0f, 0.0f, 0.0f}, kq[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-            for (int e = 0; e < PER; ++e) {
-                dq = fmaf(S[e], qq[8 * e], dq);
-                if (DELTA) dkk = fmaf(S[e], kk[8 * e], dkk);
+            for (int j = 0; j < PER / 4; ++j) {
+                const float4 qv = q4[j * 8], kv = k4[j * 8];
+                kk[4 * j] = kv.x; kk[4 * j + 1] = kv.y; kk[4 * j + 2] = kv.z; kk[4 * j + 3] = kv.w;
+                dq[0] = fmaf(S[4 * j], qv.x, dq[0]); dq[1] = fmaf(S[4 * j + 1], qv.y, dq[1]);
+                dq[2] = fmaf(S[4 * j + 2], qv.z, dq[2]); dq[3] = fmaf(S[4 * j + 3], qv.w, dq[3]);
+                kq[0] = fmaf(kv.x, qv.x, kq[0]); kq[1] = fmaf(kv.y, qv.y, kq[1]);
+                kq[2] = fmaf(kv.z, qv.z, kq[2]); kq[3] = fmaf(kv.w, qv.w, kq[3]);
+                if (DELTA) {
+                    dkk[0] = fmaf(S[4 * j], kv.x, dkk[0]); dkk[1] = fmaf(S[4 * j + 1], kv.y, dkk[1]);
+                    dkk[2] = fmaf(S[4 * j + 2], kv.z, dkk[2]); dkk[3] = fmaf(S[4 * j + 3], kv.w, dkk[3]);
+                }
             }
+            float sdq = (dq[0] + dq[1]) + (dq[2] + dq[3]), skq = (kq[0] + kq[1]) + (kq[2] + kq[3]);
+            float sdk = DELTA ? (dkk[0] + dkk[1]) + (dkk[2] + dkk[3]) : 0.0f;
 #pragma unroll
             for (int o = 1; o < 8; o <<= 1) {
-                dq += __shfl_xor_sync(0xffffffffu, dq, o);
-                if (DELTA) dkk += __shfl_xor_sync(0xffffffffu, dkk, o);
+                if (DELTA) sdk += __shfl_xor_sync(0xffffffffu, sdk, o);
+                sdq += __shfl_xor_sync(0xffffffffu, sdq, o);
+                skq += __shfl_xor_sync(0xffffffffu, skq, o);
             }
             const float g = sg[tt];
             const float vv = sv[tt * LS_COLS + cl];
-            const float u = DELTA ? sb[tt] * (vv - g * dkk) : vv;
+            const float u = DELTA ? sb[tt] * (vv - g * sdk) : vv;
 #pragma unroll
-            for (int e = 0; e < PER; ++e) S[e] = fmaf(kk[8 * e], u, g * S[e]);
-            if (ks == 0) so[tt * LS_COLS + cl] = fmaf(u, skq[tt], g * dq);     // S_new^T q = g S_old^T q + u (k . q)
+            for (int e = 0; e < PER; ++e) S[e] = fmaf(kk[e], u, g * S[e]);
+            if (ks == 0) so[tt * LS_COLS + cl] = fmaf(u, skq, g * sdq);     // S_new^T q = g S_old^T q + u (k . q)
         }
         __syncthreads();
         for (int idx = threadIdx.x; idx < cnt * LS_COLS; idx += 128) {
@@ -255,7 +387,7 @@ __global__ void __launch_bounds__(128) linear_state_walk_kernel(
     if (col_ok) {
 #pragma unroll
         for (int e = 0; e < PER; ++e) {
-            const int i = e * 8 + ks;
+            const int i = (e >> 2) * 32 + ks * 4 + (e & 3);
             if (i < dk) st[i] = S[e];
         }
     }
@@ -265,13 +397,21 @@ template <int PER>
 static void ls_walk_launch(bool delta, dim3 grid, cudaStream_t s, const float* q, const float* k, const float* v, int ldq, int ldk, int ldv,
                            const float* gate, const float* beta, const float* head_decay, float* out, float* state, long long state_stride,
                            const int32_t* req_meta, const int32_t* slots, const int32_t* positions, int H, int Gq, int dk, int dv) {
-    const size_t smem = sizeof(float) * (LS_AHEAD * (2 * 8 * PER + 2 * LS_COLS) + 3 * LS_AHEAD);
-    if (delta)
-        mm_launch(linear_state_walk_kernel<PER, true>, grid, dim3(128), smem, s, q, k, v, ldq, ldk, ldv, gate, beta, head_decay, out, state,
-                  state_stride, req_meta, slots, positions, H, Gq, dk, dv);
-    else
-        mm_launch(linear_state_walk_kernel<PER, false>, grid, dim3(128), smem, s, q, k, v, ldq, ldk, ldv, gate, beta, head_decay, out, state,
-                  state_stride, req_meta, slots, positions, H, Gq, dk, dv);
+    const size_t smem = sizeof(float) * (2 * LS_AHEAD * (2 * 8 * PER + LS_COLS + 2) + LS_AHEAD * LS_COLS);
+    // 16-byte copies where every row and head of q, k and v starts on a 16-byte boundary, 4-byte copies otherwise
+    const int vec_ok = dk % 4 == 0 && dv % 4 == 0 && ldq % 4 == 0 && ldk % 4 == 0 && ldv % 4 == 0 &&
+                       (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15) == 0;
+    if (delta) {
+        auto kernel = linear_state_walk_kernel<PER, true>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        mm_launch(kernel, grid, dim3(128), smem, s, q, k, v, ldq, ldk, ldv, gate, beta, head_decay, out, state,
+                  state_stride, req_meta, slots, positions, H, Gq, dk, dv, vec_ok);
+    } else {
+        auto kernel = linear_state_walk_kernel<PER, false>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        mm_launch(kernel, grid, dim3(128), smem, s, q, k, v, ldq, ldk, ldv, gate, beta, head_decay, out, state,
+                  state_stride, req_meta, slots, positions, H, Gq, dk, dv, vec_ok);
+    }
 }
 
 MM_EXPORT int mm_linear_state_walk(const void* q, const void* k, const void* v, int ldq, int ldk, int ldv, const void* gate,

@@ -28,15 +28,9 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {      // the larg
     }
 }
 
-__global__ void moe_route_kernel(const float* __restrict__ z, int ldz, int n_tokens, int E, int top, int groups, int keep,
-                                 int32_t* __restrict__ idx, float* __restrict__ wts) {
-    extern __shared__ float route_smem[];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-    const int t = blockIdx.x * warps + warp;
-    if (t >= n_tokens) return;
-    float* s = route_smem + (size_t)warp * (E + groups);       // scores, then the runs' scores (negative: run not kept)
-    float* gs = s + E;
-    const float* zr = z + (size_t)t * ldz;
+// One warp: the choice for one token from its E logits `zr`; s, gs: the warp's scratch (E and `groups` floats).
+__device__ __forceinline__ void moe_route_warp(const float* zr, float* s, float* gs, int lane, int E, int top, int groups, int keep,
+                                               int32_t* __restrict__ idx, float* __restrict__ wts, size_t t) {
     float m = -INFINITY;
     for (int e = lane; e < E; e += 32) m = fmaxf(m, zr[e]);
     m = warp_max(m);
@@ -58,7 +52,7 @@ __global__ void moe_route_kernel(const float* __restrict__ z, int ldz, int n_tok
             gs[g] = b;
         }
         __syncwarp();
-        // the keep best runs get their score negated and shifted below zero: what stays non-negative is dropped
+        // the keep best runs get their score replaced by -1: what stays non-negative is dropped
         for (int kk = 0; kk < keep; ++kk) {
             float bv = -1.0f;
             int bi = 0x7fffffff;
@@ -72,7 +66,7 @@ __global__ void moe_route_kernel(const float* __restrict__ z, int ldz, int n_tok
             __syncwarp();
         }
         for (int e = lane; e < E; e += 32)
-            if (gs[e / size] >= 0.0f) s[e] = -1.0f - s[e];      // not eligible; the score survives as -(1 + s)
+            if (gs[e / size] >= 0.0f) s[e] = -1.0f - s[e];      // not eligible
         __syncwarp();
     }
     float total = 0.0f;
@@ -94,15 +88,64 @@ __global__ void moe_route_kernel(const float* __restrict__ z, int ldz, int n_tok
         __syncwarp();
         total += bv;
         if (lane == 0) {
-            idx[(size_t)t * top + kk] = bi;
-            wts[(size_t)t * top + kk] = bv;
+            idx[t * top + kk] = bi;
+            wts[t * top + kk] = bv;
         }
     }
     __syncwarp();
     if (lane == 0) {
         const float d = total + 1e-20f;
-        for (int kk = 0; kk < top; ++kk) wts[(size_t)t * top + kk] /= d;
+        for (int kk = 0; kk < top; ++kk) wts[t * top + kk] /= d;
     }
+}
+
+__global__ void moe_route_kernel(const float* __restrict__ z, int ldz, int n_tokens, int E, int top, int groups, int keep,
+                                 int32_t* __restrict__ idx, float* __restrict__ wts) {
+    extern __shared__ float route_smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int t = blockIdx.x * warps + warp;
+    if (t >= n_tokens) return;
+    float* s = route_smem + (size_t)warp * (E + groups);
+    moe_route_warp(z + (size_t)t * ldz, s, s + E, lane, E, top, groups, keep, idx, wts, (size_t)t);
+}
+
+// The router's product and its choice in one launch, one block per token: every warp takes experts in turn and sums
+// x . w_e over lanes in fp32 (a fixed order, whatever else is in the batch); then the first warp chooses.
+template <typename T>
+__global__ void __launch_bounds__(128) moe_router_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ w, int D, int E, int top,
+                                                         int groups, int keep, int32_t* __restrict__ idx, float* __restrict__ wts) {
+    extern __shared__ float route_smem[];      // logits [E], scores [E], runs [groups]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t t = blockIdx.x;
+    const T* xr = x + t * ldx;
+    for (int e = warp; e < E; e += 4) {
+        const float* we = w + (size_t)e * D;
+        float acc = 0.0f;
+        for (int d = lane; d < D; d += 32) acc = fmaf(to_f32<T>(xr[d]), we[d], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) route_smem[e] = acc;
+    }
+    __syncthreads();
+    if (warp == 0) moe_route_warp(route_smem, route_smem + E, route_smem + 2 * E, lane, E, top, groups, keep, idx, wts, t);
+}
+
+MM_EXPORT int mm_moe_router(const void* x, int x_dtype, int ldx, const void* w, int n_tokens, int D, int E, int top, int groups, int keep,
+                            void* idx, void* wts, void* stream) {
+    MM_REQUIRE(n_tokens >= 0 && D > 0 && ldx >= D && E > 0 && top > 0 && top <= E && groups > 0 && E % groups == 0 && keep > 0 && keep <= groups,
+               "moe router: experts must split into equal runs, and 0 < top <= experts, 0 < keep <= runs");
+    MM_REQUIRE((size_t)(2 * E + groups) * sizeof(float) <= 48 * 1024, "moe router: too many experts for the router's shared memory");
+    if (n_tokens == 0) return MM_OK;
+    const size_t smem = (size_t)(2 * E + groups) * sizeof(float);
+    if (x_dtype == MM_F32)
+        mm_launch(moe_router_kernel<float>, dim3(n_tokens), dim3(128), smem, (cudaStream_t)stream, (const float*)x, ldx, (const float*)w, D, E, top,
+                  groups, keep, (int32_t*)idx, (float*)wts);
+    else if (x_dtype == MM_BF16)
+        mm_launch(moe_router_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(128), smem, (cudaStream_t)stream, (const __nv_bfloat16*)x, ldx,
+                  (const float*)w, D, E, top, groups, keep, (int32_t*)idx, (float*)wts);
+    else
+        MM_REQUIRE(false, "moe router: dtype must be float32 or bfloat16");
+    MM_CHECK_LAUNCH();
+    return MM_OK;
 }
 
 MM_EXPORT int mm_moe_route(const void* z, int ldz, int n_tokens, int E, int top, int groups, int keep, void* idx, void* wts, void* stream) {

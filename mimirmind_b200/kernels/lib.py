@@ -64,7 +64,9 @@ _PROTOTYPES = {
     "mm_mingru_chunked": [P, P, I, P, P, P, P, P, P, P, P, I, I, I, P],
     "mm_bias_act": [P, P, I, P, I, I, I, I, P],
     "mm_causal_conv_walk": [P, I, I, P, I, P, c_longlong, P, P, P, I, I, P],
-    "mm_linear_state_prep": [P, I, I, I, I, I, I, I, I, I, P, I, I, F, F, F, I, I, I, P, P, P, P, P],
+    "mm_linear_state_prep": [P, I, I, I, I, I, I, I, I, I, P, I, I, F, F, F, P, I, I, I, I, P, P, P, P, P],
+    "mm_causal_conv_tokens": [P, I, I, P, I, P, c_longlong, P, I, P, P, P, P, I, I, I, P],
+    "mm_moe_router": [P, I, I, P, I, I, I, I, I, I, P, P, P],
     "mm_angle_table": [P, P, P, I, I, P],
     "mm_linear_state_walk": [P, P, P, I, I, I, P, P, P, P, P, c_longlong, P, P, P, I, I, I, I, I, P],
     "mm_gated_group_norm": [P, I, I, P, I, I, P, I, P, I, I, I, I, F, I, I, P],

@@ -896,6 +896,28 @@ def causal_conv_walk(x: torch.Tensor, channels: int, taps: torch.Tensor, tail: t
     return x
 
 
+def causal_conv_tokens(x: torch.Tensor, channels: int, taps: torch.Tensor, tail: torch.Tensor, token_req: torch.Tensor,
+                       req_meta: Optional[torch.Tensor], slots: torch.Tensor, positions: torch.Tensor, n_requests: int, silu: bool = True) -> torch.Tensor:
+    """The same convolution with one thread per (token, channel), for long portions: returns a new fp32 [n, channels], leaves
+    ``x`` as it is, and then leaves every request's last K-1 inputs in ``tail``."""
+    _need(x, "conv rows", torch.float32)
+    _need(taps, "conv taps", torch.float32)
+    _need(token_req, "token_req", torch.int32)
+    _need(slots, "state slots", torch.int32)
+    _need(positions, "positions", torch.int32)
+    if tail.dtype != torch.float32 or not tail.is_cuda or tail.stride(-1) != 1:
+        raise KernelError("conv: the state is fp32 with unit stride in its last axis")
+    K = taps.shape[1]
+    if taps.shape[0] != channels or x.shape[1] < channels or tail.shape[1] < (K - 1) * channels:
+        raise KernelError("conv: shape mismatch")
+    n = x.shape[0]
+    y = torch.empty((n, channels), dtype=torch.float32, device=x.device)
+    check(_lib.load().mm_causal_conv_tokens(x.data_ptr(), x.shape[1], channels, taps.data_ptr(), K, tail.data_ptr(), tail.stride(0), y.data_ptr(),
+                                            channels, token_req.data_ptr(), _ptr(req_meta), slots.data_ptr(), positions.data_ptr(), n,
+                                            int(n_requests), int(bool(silu)), _stream()), "causal_conv_tokens")
+    return y
+
+
 def angle_table(positions: torch.Tensor, freq: torch.Tensor) -> torch.Tensor:
     """(cos, sin) of ``position * freq[i]`` as fp32 [n, len(freq), 2]."""
     _need(positions, "positions", torch.int32)
@@ -909,14 +931,18 @@ def angle_table(positions: torch.Tensor, freq: torch.Tensor) -> torch.Tensor:
 def linear_state_prep(x: torch.Tensor, q_off: int, k_off: int, v_off: int, qk_heads: int, dk: int, n_v: int, *, silu: bool = False,
                       rot: Optional[torch.Tensor] = None, rot_dims: int = 0, unit: bool = False, unit_eps: float = 0.0,
                       q_scale: float = 1.0, k_scale: float = 1.0, a_off: int = -1, b_off: int = -1, heads: int = 0,
-                      A_log: Optional[torch.Tensor] = None, dt_bias: Optional[torch.Tensor] = None):
+                      A_log: Optional[torch.Tensor] = None, dt_bias: Optional[torch.Tensor] = None, gate_rows: Optional[torch.Tensor] = None):
     """What stands between the projection and the recurrence, in place on the fp32 rows ``x`` [n, ld]: silu on q, k and v;
     rotation of the half-split pairs of q and k by ``rot`` [n, rot_dims/2, 2]; unit length of every q and k head; the
     two scales.  Returns (gate, beta), each [n, heads] fp32 or None: with ``a_off`` >= 0 the decay per token
     ``exp(-exp(A_log) softplus(a + dt_bias))`` from the row's columns ``a_off..``, with ``b_off`` >= 0 the delta rule's write
-    strength ``sigmoid(b)`` from the columns ``b_off..``."""
+    strength ``sigmoid(b)`` from the columns ``b_off..`` (of ``gate_rows`` when given: fp32 rows of their own width)."""
     _need(x, "projection rows", torch.float32)
     n, ld = x.shape
+    if gate_rows is not None:
+        _need(gate_rows, "gate rows", torch.float32)
+        if gate_rows.shape[0] != n or max(a_off, b_off) + heads > gate_rows.shape[1]:
+            raise KernelError("linear state prep: gate columns outside their row")
     gate = beta = None
     if a_off >= 0:
         _need(A_log, "A_log", torch.float32)
@@ -932,7 +958,8 @@ def linear_state_prep(x: torch.Tensor, q_off: int, k_off: int, v_off: int, qk_he
         raise KernelError("linear state prep: columns outside the row")
     check(_lib.load().mm_linear_state_prep(x.data_ptr(), ld, n, q_off, k_off, v_off, qk_heads, dk, n_v, int(bool(silu)),
                                            _ptr(rot) if rot_dims else None, int(rot_dims), int(bool(unit)), float(unit_eps),
-                                           float(q_scale), float(k_scale), int(a_off), int(b_off), int(heads), _ptr(A_log), _ptr(dt_bias),
+                                           float(q_scale), float(k_scale), _ptr(gate_rows), gate_rows.shape[1] if gate_rows is not None else 0,
+                                           int(a_off), int(b_off), int(heads), _ptr(A_log), _ptr(dt_bias),
                                            _ptr(gate), _ptr(beta), _stream()), "linear_state_prep")
     return gate, beta
 
@@ -1018,6 +1045,22 @@ def moe_route(logits: torch.Tensor, top: int, groups: int, keep: int):
     idx = torch.empty((n, top), dtype=torch.int32, device=logits.device)
     wts = torch.empty((n, top), dtype=torch.float32, device=logits.device)
     check(_lib.load().mm_moe_route(logits.data_ptr(), E, n, E, int(top), int(groups), int(keep), idx.data_ptr(), wts.data_ptr(), _stream()), "moe_route")
+    return idx, wts
+
+
+def moe_router(x: torch.Tensor, w: torch.Tensor, top: int, groups: int, keep: int):
+    """The router's product (fp32 sums over ``x`` [n, D] and the fp32 matrix ``w`` [E, D]) and its choice in one launch:
+    (experts int32 [n, top], weights fp32 [n, top])."""
+    _need(x, "router rows")
+    _need(w, "router matrix", torch.float32)
+    n, D = x.shape
+    E = w.shape[0]
+    if w.shape[1] != D:
+        raise KernelError("moe router: shape mismatch")
+    idx = torch.empty((n, top), dtype=torch.int32, device=x.device)
+    wts = torch.empty((n, top), dtype=torch.float32, device=x.device)
+    check(_lib.load().mm_moe_router(x.data_ptr(), dtype_code(x.dtype), D, w.data_ptr(), n, D, E, int(top), int(groups), int(keep), idx.data_ptr(),
+                                    wts.data_ptr(), _stream()), "moe_router")
     return idx, wts
 
 

@@ -36,6 +36,9 @@ from .base import LayerCache, Mixer, Runtime, StateSpec, StepContext, WeightView
 from .linear import linear
 
 
+CONV_BY_TOKEN_FROM = 32      # a step whose longest portion has at least this many tokens runs the convolution per (token, channel)
+
+
 @MIXERS.register("linear_state")
 class LinearStateMixer(Mixer):
     """spec params: hidden, heads, qk_heads, key_dim, value_dim, eps, the options of the module's text, and the tensor
@@ -133,7 +136,11 @@ class LinearStateMixer(Mixer):
         H, G, dk, dv = self.heads, self.qk_heads, self.dk, self.dv
         a = linear(x, self.w_in, None, self.rt, out_dtype=torch.float32)
         state = cache.state
-        if self.taps:
+        qkv, gate_rows = a, None          # where q, k and v stand, and (if elsewhere) the rows with the gates' columns
+        if self.taps and ctx.max_q_len >= CONV_BY_TOKEN_FROM:
+            qkv, gate_rows = ops.causal_conv_tokens(a, self.channels, self.conv_taps, state[:, self.state_size:], ctx.token_req, ctx.req_meta,
+                                                    ctx.state_slots, ctx.positions, ctx.n_requests, silu=self.activation == "silu"), a
+        elif self.taps:
             ops.causal_conv_walk(a, self.channels, self.conv_taps, state[:, self.state_size:], ctx.req_meta, ctx.state_slots, ctx.positions,
                                  ctx.n_requests, silu=self.activation == "silu")
         rot = None
@@ -142,11 +149,11 @@ class LinearStateMixer(Mixer):
                 ctx.derived[self.rot_key] = ops.angle_table(ctx.positions, self.freq)
             rot = ctx.derived[self.rot_key]
         gate, beta = ops.linear_state_prep(
-            a, self.q_off, self.k_off, self.v_off, G, dk, H * dv, silu=self.activation == "silu" and not self.taps, rot=rot,
+            qkv, self.q_off, self.k_off, self.v_off, G, dk, H * dv, silu=self.activation == "silu" and not self.taps, rot=rot,
             rot_dims=self.rot_dims, unit=self.unit_eps is not None, unit_eps=float(self.unit_eps or 0.0), q_scale=self.q_scale,
             k_scale=self.k_scale, a_off=self.a_off if self.learned_decay else -1, b_off=self.b_off, heads=H, A_log=self.A_log,
-            dt_bias=self.dt_bias)
-        o = ops.linear_state_walk(a[:, self.q_off:self.q_off + G * dk], a[:, self.k_off:self.k_off + G * dk], a[:, self.v_off:self.v_off + H * dv],
+            dt_bias=self.dt_bias, gate_rows=gate_rows)
+        o = ops.linear_state_walk(qkv[:, self.q_off:self.q_off + G * dk], qkv[:, self.k_off:self.k_off + G * dk], qkv[:, self.v_off:self.v_off + H * dv],
                                   state, ctx.req_meta, ctx.state_slots, ctx.positions, ctx.n_requests, H, G, dk, dv,
                                   gate=gate, beta=beta, head_decay=self.head_decay)
         g = a[:, self.g_off:self.g_off + H * dv]

@@ -19,7 +19,6 @@ from ..config.spec import PartSpec, TensorSpec
 from ..kernels import ops
 from ..registry import FEED_FORWARDS
 from .base import FeedForward, Runtime, StepContext, WeightView
-from .linear import linear
 
 
 @FEED_FORWARDS.register("routed_experts")
@@ -55,8 +54,7 @@ class RoutedExperts(FeedForward):
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         n = x.shape[0]
-        z = linear(x, self.w_router, None, self.rt, out_dtype=torch.float32)
-        idx, wts = ops.moe_route(z, self.top, self.groups, self.keep)
+        idx, wts = ops.moe_router(x, self.w_router, self.top, self.groups, self.keep)
         offsets, order = ops.moe_sort(idx, self.experts)
         tc = self.rt.matmul != "simt"
         hidden = ops.moe_gemm(x, self.w_in, offsets, order, n * self.top, self.top, True, self.rt.dtype, tensor_cores=tc)
