@@ -168,7 +168,8 @@ __device__ __forceinline__ void epilogue_rows(uint32_t taddr, int m0, int n0, in
 template <int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, void* __restrict__ out,
-                    const void* __restrict__ bias, int bias_dtype, int M, int N, int K, int ldo, int* __restrict__ err) {
+                    const void* __restrict__ bias, int bias_dtype, int M, int N, int K, int ldo, int* __restrict__ err,
+                    const int32_t* __restrict__ group_tiles, const int32_t* __restrict__ n_group_tiles, int group_w_rows) {
     extern __shared__ unsigned char smem_raw[];
     // 128-byte swizzle wants 1024-byte aligned tiles
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -203,7 +204,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     tc_fence_after();
     const uint32_t tmem_base = ctl->tmem_base;
 
-    const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN, k_blocks = (K + BK - 1) / BK;
+    // Grouped form (group_tiles given): the rows of A belong to groups that each have a weight matrix of their own, N rows
+    // of the stacked W, group_w_rows apart.  The row tiles were laid out on the device (no tile crosses a group's border):
+    // tile i covers rows group_tiles[3i] .. group_tiles[3i + 1] - 1 of group group_tiles[3i + 2]; their number is read here.
+    const bool grouped = group_tiles != nullptr;
+    const int m_tiles = grouped ? *n_group_tiles : (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN, k_blocks = (K + BK - 1) / BK;
     const int total = m_tiles * n_tiles;
 
     if (warp == 0) {
@@ -212,7 +217,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             uint32_t it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
-                const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+                const int mt = tile % m_tiles, n0 = (tile / m_tiles) * BN;
+                const int m0 = grouped ? group_tiles[3 * mt] : mt * BM;
+                const int w0 = grouped ? group_tiles[3 * mt + 2] * group_w_rows + n0 : n0;
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
@@ -221,7 +228,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     mbar_expect_tx(full, STAGE_BYTES);
                     const uint32_t a_dst = smem_u32(tiles + s * STAGE_BYTES);
                     tma_load_2d(a_dst, &tmA, kb * BK, m0, full);
-                    tma_load_2d(a_dst + A_BYTES, &tmB, kb * BK, n0, full);
+                    tma_load_2d(a_dst + A_BYTES, &tmB, kb * BK, w0, full);
                 }
             }
         }
@@ -258,12 +265,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         uint32_t local = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++local) {
-            const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+            const int mt = tile % m_tiles, n0 = (tile / m_tiles) * BN;
+            const int m0 = grouped ? group_tiles[3 * mt] : mt * BM;
+            const int m_end = grouped ? group_tiles[3 * mt + 1] : M;          // rows from here on are another group's
             const uint32_t acc = local & 1, acc_ph = (local >> 1) & 1;
             if (!mbar_wait(smem_u32(&ctl->tmem_full[acc]), acc_ph, abort_flag)) { ok = false; break; }
             tc_fence_after();
             epilogue_rows<EPI>(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN, m0, n0, q, lane, staging + q * EPI_STAGE_BYTES,
-                               out, bias, bias_dtype, M, N, ldo);
+                               out, bias, bias_dtype, m_end, N, ldo);
             // the accumulator may be overwritten once all four warps have read it
             tc_fence_before();
             __syncwarp();
@@ -462,12 +471,59 @@ int launch(const CUtensorMap& a, const CUtensorMap& b, void* out, const void* bi
     }
     const int total = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const int grid = total < max_ctas ? total : max_ctas;
-    gemm_tcgen05_kernel<EPI><<<grid, GEMM_THREADS, smem, s>>>(a, b, out, bias, bias_dtype, M, N, K, ldo, err);
+    gemm_tcgen05_kernel<EPI><<<grid, GEMM_THREADS, smem, s>>>(a, b, out, bias, bias_dtype, M, N, K, ldo, err, nullptr, nullptr, 0);
+    MM_CHECK_LAUNCH();
+    return MM_OK;
+}
+
+template <int EPI>
+int launch_grouped(const CUtensorMap& a, const CUtensorMap& b, void* out, int M, int N, int K, int ldo, int* err, int max_ctas,
+                   const int32_t* group_tiles, const int32_t* n_group_tiles, int max_group_tiles, int group_w_rows, cudaStream_t s) {
+    const size_t smem = (size_t)STAGES * STAGE_BYTES + 4 * EPI_STAGE_BYTES + 1024 + sizeof(SharedCtl);
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(gemm_tcgen05_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+            mm_set_last_error("gemm_tcgen05: cannot reserve shared memory");
+            return MM_ERR_LAUNCH;
+        }
+        configured = true;
+    }
+    const long long total = (long long)max_group_tiles * ((N + BN - 1) / BN);
+    const int grid = total < max_ctas ? (int)total : max_ctas;
+    gemm_tcgen05_kernel<EPI><<<grid, GEMM_THREADS, smem, s>>>(a, b, out, nullptr, MM_F32, M, N, K, ldo, err, group_tiles, n_group_tiles, group_w_rows);
     MM_CHECK_LAUNCH();
     return MM_OK;
 }
 
 }  // namespace
+
+// The grouped form: A [M, lda] bf16 holds the rows of `groups` groups side by side, W [groups * N, K] bf16 their weight
+// matrices one after the other; tile i of the device-made list `group_tiles` (3 ints each: first row, end row, group; at
+// most 128 rows, never across a group's border; `n_group_tiles` of them, at most `max_group_tiles`) is multiplied with
+// its group's matrix.  out [M, ldo]: bf16 [M, N], or with the SwiGLU epilogue bf16 [M, N/2].
+MM_EXPORT int mm_gemm_tcgen05_grouped(const void* A, const void* W, void* out, int epilogue, int M, int groups, int N, int K, int lda, int ldo,
+                                      const void* group_tiles, const void* n_group_tiles, int max_group_tiles, void* err, void* stream) {
+    MM_REQUIRE(M > 0 && N > 0 && K > 0 && groups > 0 && max_group_tiles > 0 && group_tiles && n_group_tiles, "gemm_tcgen05 grouped: bad sizes");
+    MM_REQUIRE(K % 8 == 0 && lda % 8 == 0 && lda >= K, "gemm_tcgen05: K and the row stride of A must be multiples of 8 (16-byte TMA rows)");
+    MM_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0 && ((uintptr_t)out & 15) == 0, "gemm_tcgen05: pointers must be 16-byte aligned");
+    MM_REQUIRE(epilogue == EPI_BF16 || epilogue == EPI_SWIGLU, "gemm_tcgen05 grouped: the epilogues are bf16 and SwiGLU");
+    MM_REQUIRE(epilogue != EPI_SWIGLU || (N % 16 == 0 && ldo >= N / 2), "gemm_tcgen05: the SwiGLU epilogue needs N a multiple of 16");
+    MM_REQUIRE(ldo % 8 == 0 && (epilogue == EPI_SWIGLU || ldo >= N), "gemm_tcgen05: the row stride of the output must be a multiple of 8 and at least N");
+    CUtensorMap ta, tb;
+    if (!tc::make_map_bf16(&ta, A, M, K, lda, BM) || !tc::make_map_bf16(&tb, W, (long long)groups * N, K, K, BN)) {
+        mm_set_last_error("gemm_tcgen05: cuTensorMapEncodeTiled failed or is not available");
+        return MM_ERR_DRIVER;
+    }
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (epilogue == EPI_SWIGLU)
+        return launch_grouped<EPI_SWIGLU>(ta, tb, out, M, N, K, ldo, (int*)err, sms, (const int32_t*)group_tiles, (const int32_t*)n_group_tiles,
+                                          max_group_tiles, N, s);
+    return launch_grouped<EPI_BF16>(ta, tb, out, M, N, K, ldo, (int*)err, sms, (const int32_t*)group_tiles, (const int32_t*)n_group_tiles,
+                                    max_group_tiles, N, s);
+}
 
 // A [M, lda] bf16 (K leading columns used), W [N, K] bf16, out [M, ldo] (bf16, fp32, or with the SwiGLU epilogue bf16
 // [M, N/2]).  `err`: device int set to 1 if a bounded wait ran out (may be null).  `pair`: the cta_group::2 kernel.

@@ -165,7 +165,12 @@ MM_EXPORT int mm_moe_route(const void* z, int ldz, int n_tokens, int E, int top,
 // ---------------------------------------------------------------------------------------------------------------
 // One block.  Rows keep their order inside an expert (a row's place is the number of rows of its expert before it), so the
 // lists are the same on every run.
-__global__ void moe_sort_kernel(const int32_t* __restrict__ idx, int n_rows, int E, int32_t* __restrict__ offsets, int32_t* __restrict__ order) {
+// Also made here, for the grouped tensor-core products: the list of row tiles (first row, end row, expert; at most
+// `tile_rows` rows, none across an expert's border) with their number, each row's token (order / top), and each
+// (token, choice)'s place in the sorted order.
+__global__ void moe_sort_kernel(const int32_t* __restrict__ idx, int n_rows, int E, int32_t* __restrict__ offsets, int32_t* __restrict__ order,
+                                int top, int tile_rows, int32_t* __restrict__ tiles, int32_t* __restrict__ n_tiles,
+                                int32_t* __restrict__ row_token, int32_t* __restrict__ place) {
     extern __shared__ int32_t sort_smem[];     // counts [E], then the running cursors [E]
     int32_t* counts = sort_smem;
     int32_t* cursor = counts + E;
@@ -181,6 +186,16 @@ __global__ void moe_sort_kernel(const int32_t* __restrict__ idx, int n_rows, int
             acc += counts[e];
         }
         offsets[E] = acc;
+        if (tiles != nullptr) {
+            int nt = 0;
+            for (int e = 0; e < E; ++e)
+                for (int lo = offsets[e]; lo < offsets[e + 1]; lo += tile_rows, ++nt) {
+                    tiles[3 * nt] = lo;
+                    tiles[3 * nt + 1] = min(lo + tile_rows, offsets[e + 1]);
+                    tiles[3 * nt + 2] = e;
+                }
+            *n_tiles = nt;
+        }
     }
     __syncthreads();
     // stable placement: the rows are taken in rounds of blockDim.x; inside a round a row's rank among the rows of its
@@ -198,16 +213,21 @@ __global__ void moe_sort_kernel(const int32_t* __restrict__ idx, int n_rows, int
                 if (lane == first) start = atomicAdd(&cursor[e], __popc(peers));
                 start = __shfl_sync(peers, start, first);
                 order[start + rank] = r;
+                if (row_token != nullptr) row_token[start + rank] = r / top;
+                if (place != nullptr) place[r] = start + rank;
             }
             __syncthreads();
         }
     }
 }
 
-MM_EXPORT int mm_moe_sort(const void* idx, int n_rows, int E, void* offsets, void* order, void* stream) {
-    MM_REQUIRE(n_rows >= 0 && E > 0 && E <= 4096, "moe sort: bad sizes");
+MM_EXPORT int mm_moe_sort(const void* idx, int n_rows, int E, void* offsets, void* order, int top, int tile_rows, void* tiles, void* n_tiles,
+                          void* row_token, void* place, void* stream) {
+    MM_REQUIRE(n_rows >= 0 && E > 0 && E <= 4096 && top > 0, "moe sort: bad sizes");
+    MM_REQUIRE(tiles == nullptr || (tile_rows > 0 && n_tiles != nullptr), "moe sort: the tile list needs its tile size and its count");
     mm_launch(moe_sort_kernel, dim3(1), dim3(n_rows > 256 ? 1024 : 256), (size_t)2 * E * sizeof(int32_t), (cudaStream_t)stream,
-              (const int32_t*)idx, n_rows, E, (int32_t*)offsets, (int32_t*)order);
+              (const int32_t*)idx, n_rows, E, (int32_t*)offsets, (int32_t*)order, top, tile_rows, (int32_t*)tiles, (int32_t*)n_tiles,
+              (int32_t*)row_token, (int32_t*)place);
     MM_CHECK_LAUNCH();
     return MM_OK;
 }
@@ -335,7 +355,7 @@ __global__ void __launch_bounds__(256) moe_gemm_simt_kernel(const TA* __restrict
 template <bool GATED, typename TC>
 __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ W,
                                                            TC* __restrict__ C, int ldc, const int32_t* __restrict__ offsets,
-                                                           const int32_t* __restrict__ order, int E, int top, int N, int K) {
+                                                           const int32_t* __restrict__ order, int E, int top, int N, int K, int interleaved) {
     constexpr int BK = 32, LD = BK + 8;      // 80-byte rows: ldmatrix reads without bank conflicts
     __shared__ __align__(16) __nv_bfloat16 As[2][MOE_BM][LD];
     __shared__ __align__(16) __nv_bfloat16 Ws[2][GATED ? 2 * MOE_BN : MOE_BN][LD];
@@ -380,8 +400,11 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const __nv_bfloat16* 
         }
         for (int i = tid; i < WROWS * 4; i += 128) {
             const int r = i >> 2, c = (i & 3) * 8;
-            const int n = GATED ? (r < MOE_BN ? n0 + r : N + n0 + (r - MOE_BN)) : n0 + r;
-            const bool ok = (GATED ? (r < MOE_BN ? n0 + r : n0 + r - MOE_BN) : n0 + r) < N;
+            // gated: column j of the gate is row j of the expert's matrix and the up column row N + j, or, interleaved in
+            // blocks of 8 (the layout the tensor-memory product's epilogue wants), rows 16 (j / 8) + j % 8 and + 8
+            const int j = GATED ? (r < MOE_BN ? n0 + r : n0 + r - MOE_BN) : n0 + r;
+            const int n = !GATED ? j : (interleaved ? 16 * (j >> 3) + (j & 7) + (r < MOE_BN ? 0 : 8) : (r < MOE_BN ? j : N + j));
+            const bool ok = j < N;
             __nv_bfloat16* dst = &Ws[stage][r][c];
             if (ok && k0 + c < K) cp_async16(dst, We + (size_t)n * K + k0 + c);
             else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
@@ -450,8 +473,10 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const __nv_bfloat16* 
 // A [rows, lda] (gated: the step's tokens; else the sorted hidden rows), W the experts' stacked matrices, C: gated
 // [n_rows, N] in sorted order, else [n_rows, N] with row order[i] written.  n_rows = tokens * top.
 MM_EXPORT int mm_moe_gemm(const void* A, int a_dtype, int lda, const void* W, int w_dtype, void* C, int c_dtype, int ldc, const void* offsets,
-                          const void* order, int n_rows, int E, int top, int N, int K, int gated, int tensor_cores, void* stream) {
+                          const void* order, int n_rows, int E, int top, int N, int K, int gated, int tensor_cores, int interleaved,
+                          void* stream) {
     MM_REQUIRE(n_rows >= 0 && E > 0 && top > 0 && N > 0 && K > 0 && lda >= K && ldc >= N, "moe gemm: bad sizes");
+    MM_REQUIRE(!interleaved || (gated && N % 8 == 0), "moe gemm: interleaved gate and up rows need a gated product of a multiple of 8 columns");
     if (n_rows == 0) return MM_OK;
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid(ceil_div(N, MOE_BN), ceil_div(n_rows, MOE_BM) + E);
@@ -460,16 +485,17 @@ MM_EXPORT int mm_moe_gemm(const void* A, int a_dtype, int lda, const void* W, in
     const int32_t* ord = (const int32_t*)order;
     if (tensor_cores && a_dtype == MM_BF16 && w_dtype == MM_BF16 && K % 8 == 0 && lda % 8 == 0 && ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0) {
         if (gated && c_dtype == MM_BF16)
-            mm_launch(moe_gemm_mma_kernel<true, bf>, grid, dim3(128), 0, s, (const bf*)A, lda, (const bf*)W, (bf*)C, ldc, off, ord, E, top, N, K);
+            mm_launch(moe_gemm_mma_kernel<true, bf>, grid, dim3(128), 0, s, (const bf*)A, lda, (const bf*)W, (bf*)C, ldc, off, ord, E, top, N, K, interleaved);
         else if (!gated && c_dtype == MM_BF16)
-            mm_launch(moe_gemm_mma_kernel<false, bf>, grid, dim3(128), 0, s, (const bf*)A, lda, (const bf*)W, (bf*)C, ldc, off, ord, E, top, N, K);
+            mm_launch(moe_gemm_mma_kernel<false, bf>, grid, dim3(128), 0, s, (const bf*)A, lda, (const bf*)W, (bf*)C, ldc, off, ord, E, top, N, K, 0);
         else if (!gated && c_dtype == MM_F32)
-            mm_launch(moe_gemm_mma_kernel<false, float>, grid, dim3(128), 0, s, (const bf*)A, lda, (const bf*)W, (float*)C, ldc, off, ord, E, top, N, K);
+            mm_launch(moe_gemm_mma_kernel<false, float>, grid, dim3(128), 0, s, (const bf*)A, lda, (const bf*)W, (float*)C, ldc, off, ord, E, top, N, K, 0);
         else
             MM_REQUIRE(false, "moe gemm: this combination of dtypes is not built");
         MM_CHECK_LAUNCH();
         return MM_OK;
     }
+    MM_REQUIRE(!interleaved, "moe gemm: interleaved gate and up rows are read by the tensor-core kernels only");
 #define MOE_SIMT(TA, TW, TC)                                                                                                                  \
     do {                                                                                                                                      \
         if (gated)                                                                                                                            \
@@ -486,29 +512,35 @@ MM_EXPORT int mm_moe_gemm(const void* A, int a_dtype, int lda, const void* W, in
     return MM_OK;
 }
 
-// out[t, :] = sum over the token's choices c, in order, of wts[t, c] * y[t * top + c, :]
+// out[t, :] = sum over the token's choices c, in order, of wts[t, c] * y[row(t, c), :], row(t, c) = t * top + c or, when
+// y stands in sorted order, place[t * top + c]
 template <typename TY, typename TO>
-__global__ void moe_combine_kernel(const TY* __restrict__ y, const float* __restrict__ wts, TO* __restrict__ out, int top, int d) {
+__global__ void moe_combine_kernel(const TY* __restrict__ y, const float* __restrict__ wts, const int32_t* __restrict__ place, TO* __restrict__ out,
+                                   int top, int d) {
     const size_t t = blockIdx.x;
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
         float acc = 0.0f;
-        for (int c = 0; c < top; ++c) acc = fmaf(wts[t * top + c], to_f32<TY>(y[(t * top + c) * d + i]), acc);
+        for (int c = 0; c < top; ++c) {
+            const size_t row = place ? (size_t)place[t * top + c] : t * top + c;
+            acc = fmaf(wts[t * top + c], to_f32<TY>(y[row * d + i]), acc);
+        }
         out[t * d + i] = from_f32<TO>(acc);
     }
 }
 
-MM_EXPORT int mm_moe_combine(const void* y, int y_dtype, const void* wts, void* out, int out_dtype, int n_tokens, int top, int d, void* stream) {
+MM_EXPORT int mm_moe_combine(const void* y, int y_dtype, const void* wts, const void* place, void* out, int out_dtype, int n_tokens, int top, int d,
+                             void* stream) {
     MM_REQUIRE(n_tokens >= 0 && top > 0 && d > 0, "moe combine: bad sizes");
     if (n_tokens == 0) return MM_OK;
     cudaStream_t s = (cudaStream_t)stream;
     typedef __nv_bfloat16 bf;
     const dim3 grid(n_tokens), block(d >= 1024 ? 256 : 128);
     if (y_dtype == MM_F32 && out_dtype == MM_F32)
-        mm_launch(moe_combine_kernel<float, float>, grid, block, 0, s, (const float*)y, (const float*)wts, (float*)out, top, d);
+        mm_launch(moe_combine_kernel<float, float>, grid, block, 0, s, (const float*)y, (const float*)wts, (const int32_t*)place, (float*)out, top, d);
     else if (y_dtype == MM_F32 && out_dtype == MM_BF16)
-        mm_launch(moe_combine_kernel<float, bf>, grid, block, 0, s, (const float*)y, (const float*)wts, (bf*)out, top, d);
+        mm_launch(moe_combine_kernel<float, bf>, grid, block, 0, s, (const float*)y, (const float*)wts, (const int32_t*)place, (bf*)out, top, d);
     else if (y_dtype == MM_BF16 && out_dtype == MM_BF16)
-        mm_launch(moe_combine_kernel<bf, bf>, grid, block, 0, s, (const bf*)y, (const float*)wts, (bf*)out, top, d);
+        mm_launch(moe_combine_kernel<bf, bf>, grid, block, 0, s, (const bf*)y, (const float*)wts, (const int32_t*)place, (bf*)out, top, d);
     else
         MM_REQUIRE(false, "moe combine: this combination of dtypes is not built");
     MM_CHECK_LAUNCH();

@@ -72,9 +72,10 @@ _PROTOTYPES = {
     "mm_gated_group_norm": [P, I, I, P, I, I, P, I, P, I, I, I, I, F, I, I, P],
     "mm_normed_mean2": [P, P, P, P, P, I, I, I, F, F, P],
     "mm_moe_route": [P, I, I, I, I, I, I, P, P, P],
-    "mm_moe_sort": [P, I, I, P, P, P],
-    "mm_moe_gemm": [P, I, I, P, I, P, I, I, P, P, I, I, I, I, I, I, I, P],
-    "mm_moe_combine": [P, I, P, P, I, I, I, I, P],
+    "mm_moe_sort": [P, I, I, P, P, I, I, P, P, P, P, P],
+    "mm_moe_gemm": [P, I, I, P, I, P, I, I, P, P, I, I, I, I, I, I, I, I, P],
+    "mm_moe_combine": [P, I, P, P, P, I, I, I, I, P],
+    "mm_gemm_tcgen05_grouped": [P, P, P, I, I, I, I, I, I, I, P, P, I, P, P],
 }
 
 

@@ -1064,38 +1064,85 @@ def moe_router(x: torch.Tensor, w: torch.Tensor, top: int, groups: int, keep: in
     return idx, wts
 
 
-def moe_sort(idx: torch.Tensor, experts: int):
-    """Rows (token * top + choice) put side by side by expert: (offsets int32 [E + 1], order int32 [rows])."""
+MOE_TILE_ROWS = 128       # rows of a tile of the grouped tensor-memory product
+
+
+@dataclass
+class ExpertRows:
+    """The step's (token, choice) rows put side by side by expert: ``offsets`` int32 [E + 1]; ``order`` int32 [rows]: the
+    row (token * top + choice) at every place; and, when asked for, the row tiles of the grouped tensor-memory product
+    (``tiles`` int32 [max_tiles, 3] = first row, end row, expert; ``n_tiles`` int32 [1]), every place's token
+    (``row_token``) and every row's place (``place``)."""
+
+    offsets: torch.Tensor
+    order: torch.Tensor
+    tiles: Optional[torch.Tensor] = None
+    n_tiles: Optional[torch.Tensor] = None
+    max_tiles: int = 0
+    row_token: Optional[torch.Tensor] = None
+    place: Optional[torch.Tensor] = None
+
+
+def moe_sort(idx: torch.Tensor, experts: int, with_tiles: bool = False) -> ExpertRows:
+    """Rows (token * top + choice) put side by side by expert, in their order within an expert."""
     _need(idx, "expert choice", torch.int32)
-    rows = idx.numel()
-    offsets = torch.empty((experts + 1,), dtype=torch.int32, device=idx.device)
-    order = torch.empty((max(rows, 1),), dtype=torch.int32, device=idx.device)
-    check(_lib.load().mm_moe_sort(idx.data_ptr(), rows, int(experts), offsets.data_ptr(), order.data_ptr(), _stream()), "moe_sort")
-    return offsets, order
+    rows, top = idx.numel(), idx.shape[-1]
+    dev = idx.device
+    out = ExpertRows(torch.empty((experts + 1,), dtype=torch.int32, device=dev), torch.empty((max(rows, 1),), dtype=torch.int32, device=dev))
+    if with_tiles:
+        out.max_tiles = -(-rows // MOE_TILE_ROWS) + experts
+        out.tiles = torch.empty((out.max_tiles, 3), dtype=torch.int32, device=dev)
+        out.n_tiles = torch.empty((1,), dtype=torch.int32, device=dev)
+        out.row_token = torch.empty((max(rows, 1),), dtype=torch.int32, device=dev)
+        out.place = torch.empty((max(rows, 1),), dtype=torch.int32, device=dev)
+    check(_lib.load().mm_moe_sort(idx.data_ptr(), rows, int(experts), out.offsets.data_ptr(), out.order.data_ptr(), int(top), MOE_TILE_ROWS,
+                                  _ptr(out.tiles), _ptr(out.n_tiles), _ptr(out.row_token), _ptr(out.place), _stream()), "moe_sort")
+    return out
 
 
-def moe_gemm(a: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, order: torch.Tensor, n_rows: int, top: int, gated: bool,
-             out_dtype: torch.dtype, tensor_cores: bool = True) -> torch.Tensor:
+def moe_gemm(a: torch.Tensor, w: torch.Tensor, rows: ExpertRows, n_rows: int, top: int, gated: bool,
+             out_dtype: torch.dtype, tensor_cores: bool = True, interleaved: bool = False) -> torch.Tensor:
     """The experts' products over their rows.  ``gated``: ``a`` [tokens, K] are the step's rows, ``w`` [E, 2F, K] the gate's
-    rows then the up rows of every expert, result ``silu(gate) * up`` [n_rows, F] in sorted order.  Otherwise ``a``
-    [n_rows, K] are sorted rows, ``w`` [E, N, K], and row ``order[i]`` of the result [n_rows, N] gets sorted row i's product."""
+    rows then the up rows of every expert (``interleaved``: alternating in blocks of 8), result ``silu(gate) * up``
+    [n_rows, F] in sorted order.  Otherwise ``a`` [n_rows, K] are sorted rows, ``w`` [E, N, K], and row ``order[i]`` of the
+    result [n_rows, N] gets sorted row i's product."""
     _need(a, "moe rows")
     _need(w, "moe weights", a.dtype)
-    _need(offsets, "moe offsets", torch.int32)
-    _need(order, "moe order", torch.int32)
     E, rows_w, K = w.shape
     N = rows_w // 2 if gated else rows_w
     if a.shape[1] != K or (not gated and a.shape[0] != n_rows):
         raise KernelError("moe gemm: shape mismatch")
     out = torch.empty((n_rows, N), dtype=out_dtype, device=a.device)
     check(_lib.load().mm_moe_gemm(a.data_ptr(), dtype_code(a.dtype), a.stride(0), w.data_ptr(), dtype_code(w.dtype), out.data_ptr(),
-                                  dtype_code(out_dtype), N, offsets.data_ptr(), order.data_ptr(), int(n_rows), E, int(top), N, K,
-                                  int(bool(gated)), int(bool(tensor_cores)), _stream()), "moe_gemm")
+                                  dtype_code(out_dtype), N, rows.offsets.data_ptr(), rows.order.data_ptr(), int(n_rows), E, int(top), N, K,
+                                  int(bool(gated)), int(bool(tensor_cores)), int(bool(interleaved)), _stream()), "moe_gemm")
     return out
 
 
-def moe_combine(y: torch.Tensor, wts: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
-    """``out[t] = sum_c wts[t, c] * y[t * top + c]`` in the order of the choice."""
+def moe_gemm_grouped_supported(n_rows: int, n: int, k: int) -> bool:
+    return n_rows > 0 and k % 8 == 0 and n % 16 == 0
+
+
+def moe_gemm_grouped(a: torch.Tensor, w: torch.Tensor, rows: ExpertRows, swiglu: bool) -> torch.Tensor:
+    """The grouped tensor-memory product: ``a`` [n_rows, K] bf16 in sorted order, ``w`` [E, N, K] bf16; every row tile of
+    ``rows.tiles`` times its expert's matrix.  ``swiglu``: the matrix interleaves gate and up rows in blocks of 8 and the
+    result is ``silu(gate) * up`` [n_rows, N/2]; else [n_rows, N].  bf16, in sorted order."""
+    _need(a, "moe rows", torch.bfloat16)
+    _need(w, "moe weights", torch.bfloat16)
+    if rows.tiles is None:
+        raise KernelError("moe gemm: the rows were sorted without their tile list")
+    n_rows, K = a.shape
+    E, N, _ = w.shape
+    out = torch.empty((n_rows, N // 2 if swiglu else N), dtype=torch.bfloat16, device=a.device)
+    check(_lib.load().mm_gemm_tcgen05_grouped(a.data_ptr(), w.data_ptr(), out.data_ptr(), 1 if swiglu else 0, n_rows, E, N, K, K, out.shape[1],
+                                              rows.tiles.data_ptr(), rows.n_tiles.data_ptr(), rows.max_tiles,
+                                              tcgen05_error_flag(a.device).data_ptr(), _stream()), "gemm_tcgen05_grouped")
+    return out
+
+
+def moe_combine(y: torch.Tensor, wts: torch.Tensor, out_dtype: torch.dtype, place: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[t] = sum_c wts[t, c] * y[row(t, c)]`` in the order of the choice; ``row(t, c) = t * top + c``, or
+    ``place[t * top + c]`` when ``y`` stands in sorted order."""
     _need(y, "moe outputs")
     _need(wts, "moe weights", torch.float32)
     n, top = wts.shape
@@ -1103,6 +1150,6 @@ def moe_combine(y: torch.Tensor, wts: torch.Tensor, out_dtype: torch.dtype) -> t
     if y.shape[0] != n * top:
         raise KernelError("moe combine: shape mismatch")
     out = torch.empty((n, d), dtype=out_dtype, device=y.device)
-    check(_lib.load().mm_moe_combine(y.data_ptr(), dtype_code(y.dtype), wts.data_ptr(), out.data_ptr(), dtype_code(out_dtype), n, top, d, _stream()),
-          "moe_combine")
+    check(_lib.load().mm_moe_combine(y.data_ptr(), dtype_code(y.dtype), wts.data_ptr(), _ptr(place), out.data_ptr(), dtype_code(out_dtype), n, top, d,
+                                     _stream()), "moe_combine")
     return out

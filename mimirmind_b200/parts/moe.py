@@ -5,9 +5,11 @@ scored by its best expert and only the ``keep`` best runs are eligible; the ``to
 are chosen and weighted by ``s / (sum of the chosen s + 1e-20)``.  Expert: ``W_down (silu(W_gate h) ⊙ W_up h)``, no biases.
 The output is the weighted sum of the chosen experts' outputs.
 
-The experts' matrices are stacked at load (``[E, 2F, D]`` gate rows then up rows, ``[E, D, F]``).  A step routes on the
-device, puts the rows of every expert side by side, and runs two grouped products over them (``csrc/moe.cu``); nothing
-waits for the host, so a decode step with this feed-forward can be captured.
+The experts' matrices are stacked at load (``[E, 2F, D]`` gate and up rows, ``[E, D, F]``).  A step routes on the
+device, puts the rows of every expert side by side, and runs two grouped products over them: for prompt-sized steps in
+bfloat16 the tcgen05 product over row tiles laid out on the device (``csrc/gemm_tcgen05.cu``, SwiGLU in its epilogue),
+otherwise the ``mma.sync`` or fp32 kernels of ``csrc/moe.cu``.  Nothing waits for the host, so a decode step with this
+feed-forward can be captured.
 """
 from __future__ import annotations
 
@@ -19,6 +21,13 @@ from ..config.spec import PartSpec, TensorSpec
 from ..kernels import ops
 from ..registry import FEED_FORWARDS
 from .base import FeedForward, Runtime, StepContext, WeightView
+
+
+GROUPED_MIN_ROWS = 1024      # (token, choice) rows from which a step's expert products run on tensor memory
+
+
+def ctx_plain(ctx) -> bool:
+    return ctx is not None and getattr(ctx, "plain_only", False)
 
 
 @FEED_FORWARDS.register("routed_experts")
@@ -44,9 +53,17 @@ class RoutedExperts(FeedForward):
             raise ValueError("routed experts: the experts split into equal runs, 0 < keep <= runs, and top fits into the kept runs")
         self.w_router = weights.take(spec["router"]).float().contiguous()        # the router runs in fp32
         stacked_in, stacked_out = [], []
+        f, d = self.ff, self.hidden
+        # bfloat16 with sizes the tensor-memory product takes: gate and up rows alternate in blocks of 8, so that a tile of
+        # the product holds a gate value beside its up value and the activation is the product's epilogue
+        self.interleaved = (rt.dtype == torch.bfloat16 and rt.matmul != "simt" and f % 8 == 0 and d % 8 == 0)
         for e in range(self.experts):
             stem = spec["expert"].format(e)
-            stacked_in.append(torch.cat([weights.take(stem + ".gate"), weights.take(stem + ".up")], dim=0))
+            gate, up = weights.take(stem + ".gate"), weights.take(stem + ".up")
+            if self.interleaved:
+                stacked_in.append(torch.stack([gate.view(f // 8, 8, d), up.view(f // 8, 8, d)], dim=1).reshape(2 * f, d))
+            else:
+                stacked_in.append(torch.cat([gate, up], dim=0))
             stacked_out.append(weights.take(stem + ".down"))
         self.w_in = torch.stack(stacked_in).to(rt.dtype).contiguous()       # [E, 2F, D]
         self.w_out = torch.stack(stacked_out).to(rt.dtype).contiguous()     # [E, D, F]
@@ -55,8 +72,18 @@ class RoutedExperts(FeedForward):
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         n = x.shape[0]
         idx, wts = ops.moe_router(x, self.w_router, self.top, self.groups, self.keep)
-        offsets, order = ops.moe_sort(idx, self.experts)
+        n_rows = n * self.top
+        if self.interleaved and n_rows >= GROUPED_MIN_ROWS and not ctx_plain(ctx):
+            # prompt-sized: the rows are copied into sorted order once, and both products run on tensor memory over tiles of
+            # 128 rows of one expert; the outputs stay in sorted order and the weighted sum fetches them by place
+            rows = ops.moe_sort(idx, self.experts, with_tiles=True)
+            sorted_x = torch.empty((n_rows, self.hidden), dtype=x.dtype, device=x.device)
+            ops.gather_rows(x, rows.row_token, sorted_x)
+            hidden = ops.moe_gemm_grouped(sorted_x, self.w_in, rows, swiglu=True)
+            y = ops.moe_gemm_grouped(hidden, self.w_out, rows, swiglu=False)
+            return ops.moe_combine(y, wts, self.rt.dtype, place=rows.place)
+        rows = ops.moe_sort(idx, self.experts)
         tc = self.rt.matmul != "simt"
-        hidden = ops.moe_gemm(x, self.w_in, offsets, order, n * self.top, self.top, True, self.rt.dtype, tensor_cores=tc)
-        y = ops.moe_gemm(hidden, self.w_out, offsets, order, n * self.top, self.top, False, torch.float32, tensor_cores=tc)
+        hidden = ops.moe_gemm(x, self.w_in, rows, n_rows, self.top, True, self.rt.dtype, tensor_cores=tc, interleaved=self.interleaved)
+        y = ops.moe_gemm(hidden, self.w_out, rows, n_rows, self.top, False, torch.float32, tensor_cores=tc)
         return ops.moe_combine(y, wts, self.rt.dtype)

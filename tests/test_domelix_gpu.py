@@ -234,14 +234,18 @@ def test_the_routers_choice(E, top, groups, keep):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("grouped_from", [1, 1024])
 @pytest.mark.parametrize("n,d,ff,E,top,groups,keep", [(70, 64, 40, 6, 2, 3, 2), (1, 54, 33, 5, 5, 1, 1), (300, 128, 64, 8, 3, 1, 1), (9, 256, 96, 12, 4, 2, 1),
-                                                      (1500, 64, 24, 4, 1, 1, 1)])
-def test_routed_experts_against_the_plain_ones(n, d, ff, E, top, groups, keep, dtype):
+                                                      (1500, 64, 24, 4, 1, 1, 1), (700, 320, 136, 8, 3, 2, 1)])
+def test_routed_experts_against_the_plain_ones(n, d, ff, E, top, groups, keep, dtype, grouped_from, monkeypatch):
     """The feed-forward part alone: route, rows by expert, the two grouped products, the weighted sum; with and without
     the tensor cores.  The router's input is given in both as the same bfloat16-rounded rows, so the choice is the same."""
     from mimirmind_b200.config.spec import PartSpec
     from mimirmind_b200.parts.base import Runtime, WeightView
+    from mimirmind_b200.kernels import ops
+    from mimirmind_b200.parts import moe
     from mimirmind_b200.parts.moe import RoutedExperts
+    monkeypatch.setattr(moe, "GROUPED_MIN_ROWS", grouped_from)      # 1: also a handful of rows take the tensor-memory products
     rng = np.random.RandomState(n + d)
     w = {"router": bf16_round(rng.randn(E, d) * 4 / math.sqrt(d))}
     for e in range(E):
@@ -256,6 +260,7 @@ def test_routed_experts_against_the_plain_ones(n, d, ff, E, top, groups, keep, d
         got = part.forward(dev(x, DT[dtype]), None).float().cpu().numpy()
         err = rel_rms(got, want)
         assert err.max() <= (1e-5 if dtype == "float32" else 2e-2), f"{matmul}: row {int(err.argmax())}"
+    ops.check_tcgen05_errors(torch.device(DEV))
 
 
 def test_rows_by_expert_keep_their_order():
@@ -263,11 +268,20 @@ def test_rows_by_expert_keep_their_order():
     rng = np.random.RandomState(5)
     for rows, E in ((1, 3), (40, 7), (5000, 12), (3000, 300)):
         idx = rng.randint(0, E, size=rows)
-        offsets, order = ops.moe_sort(i32(idx.tolist()), E)
-        offsets, order = offsets.cpu().numpy(), order.cpu().numpy()[:rows]
+        top = 1 if rows % 2 else 2
+        res = ops.moe_sort(i32(idx.reshape(-1, top).tolist()), E, with_tiles=True)
+        offsets, order = res.offsets.cpu().numpy(), res.order.cpu().numpy()[:rows]
         assert offsets[0] == 0 and offsets[-1] == rows
         for e in range(E):
             assert order[offsets[e]:offsets[e + 1]].tolist() == np.nonzero(idx == e)[0].tolist()
+        assert res.row_token.cpu().numpy()[:rows].tolist() == (order // top).tolist()
+        assert res.place.cpu().numpy()[order].tolist() == list(range(rows))
+        # the row tiles: in order, at most 128 rows, never across an expert's border, every row in exactly one
+        n_tiles = int(res.n_tiles.item())
+        tiles = res.tiles.cpu().numpy()[:n_tiles]
+        assert n_tiles <= res.max_tiles and tiles[0, 0] == 0 and tiles[-1, 1] == rows
+        for i, (lo, hi, e) in enumerate(tiles):
+            assert 0 < hi - lo <= 128 and offsets[e] <= lo and hi <= offsets[e + 1] and (i == 0 or lo == tiles[i - 1, 1])
 
 
 # ---- attention with a distance bias and a learned sink ----------------------------------------------------------------------
