@@ -252,12 +252,18 @@ __device__ __forceinline__ void ls_cp_commit() { asm volatile("cp.async.commit_g
 template <int N>
 __device__ __forceinline__ void ls_cp_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
-template <int PER, bool DELTA>
+//
+// MODE 0: a request's tokens from its slot's state, which is left updated.  Long portions without the delta rule are cut
+// into chunks that are walked side by side (the state's update is linear: S_end = (product of the decays) S_start + what
+// the chunk adds): MODE 1 walks chunk blockIdx.z from zero and leaves what it adds, and the product of its decays, in
+// scratch; a carry kernel then walks each request's chunks in order, leaves every chunk's starting state in scratch and
+// the last state in the slot; MODE 2 walks every chunk again from its starting state and writes the outputs.
+template <int PER, bool DELTA, int MODE>
 __global__ void __launch_bounds__(128) linear_state_walk_kernel(
     const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, int ldq, int ldk, int ldv,
     const float* __restrict__ gate, const float* __restrict__ beta, const float* __restrict__ head_decay, float* __restrict__ out,
     float* __restrict__ state, long long state_stride, const int32_t* __restrict__ req_meta, const int32_t* __restrict__ slots,
-    const int32_t* __restrict__ positions, int H, int Gq, int dk, int dv, int vec_ok) {
+    const int32_t* __restrict__ positions, int H, int Gq, int dk, int dv, int vec_ok, float* __restrict__ chunk_gain) {
     constexpr int DKP = 8 * PER;
     constexpr int ROUND = LS_AHEAD * (2 * DKP + LS_COLS + 2);      // floats of one buffer: q, k, v, decay, write strength
     extern __shared__ __align__(16) float ls_smem[];
@@ -270,11 +276,13 @@ __global__ void __launch_bounds__(128) linear_state_walk_kernel(
     const int col = col0 + cl;
     const bool col_ok = col < dv;
     const int gq = h / (H / Gq);
+    // MODE 1, 2: r is a chunk, req_meta the chunk list (first token, tokens, ., .), state the scratch with one matrix set per chunk
     const int t0 = req_meta ? req_meta[4 * r] : r;
     const int n = req_meta ? req_meta[4 * r + 1] : 1;
-    float* st = state + (size_t)slots[r] * state_stride + ((size_t)h * dv + (col_ok ? col : 0)) * dk;
-    const bool fresh = positions[t0] == 0;
+    float* st = state + (size_t)(MODE == 0 ? slots[r] : r) * state_stride + ((size_t)h * dv + (col_ok ? col : 0)) * dk;
+    const bool fresh = MODE == 1 || (MODE == 0 && positions[t0] == 0);
     const float hd = head_decay ? head_decay[h] : 1.0f;
+    float gain = 1.0f;
 
     float S[PER];
 #pragma unroll
@@ -365,25 +373,31 @@ __global__ void __launch_bounds__(128) linear_state_walk_kernel(
             }
             float sdq = (dq[0] + dq[1]) + (dq[2] + dq[3]), skq = (kq[0] + kq[1]) + (kq[2] + kq[3]);
             float sdk = DELTA ? (dkk[0] + dkk[1]) + (dkk[2] + dkk[3]) : 0.0f;
+            if (MODE != 1) {
 #pragma unroll
-            for (int o = 1; o < 8; o <<= 1) {
-                if (DELTA) sdk += __shfl_xor_sync(0xffffffffu, sdk, o);
-                sdq += __shfl_xor_sync(0xffffffffu, sdq, o);
-                skq += __shfl_xor_sync(0xffffffffu, skq, o);
+                for (int o = 1; o < 8; o <<= 1) {
+                    if (DELTA) sdk += __shfl_xor_sync(0xffffffffu, sdk, o);
+                    sdq += __shfl_xor_sync(0xffffffffu, sdq, o);
+                    skq += __shfl_xor_sync(0xffffffffu, skq, o);
+                }
             }
             const float g = sg[tt];
             const float vv = sv[tt * LS_COLS + cl];
             const float u = DELTA ? sb[tt] * (vv - g * sdk) : vv;
 #pragma unroll
             for (int e = 0; e < PER; ++e) S[e] = fmaf(kk[e], u, g * S[e]);
-            if (ks == 0) so[tt * LS_COLS + cl] = fmaf(u, skq, g * sdq);     // S_new^T q = g S_old^T q + u (k . q)
+            if (MODE == 1) gain *= g;
+            if (MODE != 1 && ks == 0) so[tt * LS_COLS + cl] = fmaf(u, skq, g * sdq);     // S_new^T q = g S_old^T q + u (k . q)
         }
         __syncthreads();
-        for (int idx = threadIdx.x; idx < cnt * LS_COLS; idx += 128) {
-            const int tt = idx / LS_COLS, c = idx - tt * LS_COLS;
-            if (col0 + c < dv) out[(size_t)(t0 + base + tt) * H * dv + h * dv + col0 + c] = so[idx];
-        }
+        if (MODE != 1)
+            for (int idx = threadIdx.x; idx < cnt * LS_COLS; idx += 128) {
+                const int tt = idx / LS_COLS, c = idx - tt * LS_COLS;
+                if (col0 + c < dv) out[(size_t)(t0 + base + tt) * H * dv + h * dv + col0 + c] = so[idx];
+            }
     }
+    if (MODE == 1 && blockIdx.x == 0 && threadIdx.x == 0) chunk_gain[(size_t)r * H + h] = gain;
+    if (MODE == 2) return;
     if (col_ok) {
 #pragma unroll
         for (int e = 0; e < PER; ++e) {
@@ -393,25 +407,34 @@ __global__ void __launch_bounds__(128) linear_state_walk_kernel(
     }
 }
 
+template <int PER, bool DELTA, int MODE>
+static void ls_walk_launch_one(dim3 grid, cudaStream_t s, size_t smem, const float* q, const float* k, const float* v, int ldq, int ldk, int ldv,
+                               const float* gate, const float* beta, const float* head_decay, float* out, float* state, long long state_stride,
+                               const int32_t* req_meta, const int32_t* slots, const int32_t* positions, int H, int Gq, int dk, int dv, int vec_ok,
+                               float* chunk_gain) {
+    auto kernel = linear_state_walk_kernel<PER, DELTA, MODE>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    mm_launch(kernel, grid, dim3(128), smem, s, q, k, v, ldq, ldk, ldv, gate, beta, head_decay, out, state, state_stride, req_meta, slots,
+              positions, H, Gq, dk, dv, vec_ok, chunk_gain);
+}
+
+// mode 0 with or without the delta rule; modes 1 and 2 (chunks) without it
 template <int PER>
-static void ls_walk_launch(bool delta, dim3 grid, cudaStream_t s, const float* q, const float* k, const float* v, int ldq, int ldk, int ldv,
+static void ls_walk_launch(bool delta, int mode, dim3 grid, cudaStream_t s, const float* q, const float* k, const float* v, int ldq, int ldk, int ldv,
                            const float* gate, const float* beta, const float* head_decay, float* out, float* state, long long state_stride,
-                           const int32_t* req_meta, const int32_t* slots, const int32_t* positions, int H, int Gq, int dk, int dv) {
+                           const int32_t* req_meta, const int32_t* slots, const int32_t* positions, int H, int Gq, int dk, int dv,
+                           float* chunk_gain) {
     const size_t smem = sizeof(float) * (2 * LS_AHEAD * (2 * 8 * PER + LS_COLS + 2) + LS_AHEAD * LS_COLS);
     // 16-byte copies where every row and head of q, k and v starts on a 16-byte boundary, 4-byte copies otherwise
     const int vec_ok = dk % 4 == 0 && dv % 4 == 0 && ldq % 4 == 0 && ldk % 4 == 0 && ldv % 4 == 0 &&
                        (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15) == 0;
-    if (delta) {
-        auto kernel = linear_state_walk_kernel<PER, true>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        mm_launch(kernel, grid, dim3(128), smem, s, q, k, v, ldq, ldk, ldv, gate, beta, head_decay, out, state,
-                  state_stride, req_meta, slots, positions, H, Gq, dk, dv, vec_ok);
-    } else {
-        auto kernel = linear_state_walk_kernel<PER, false>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        mm_launch(kernel, grid, dim3(128), smem, s, q, k, v, ldq, ldk, ldv, gate, beta, head_decay, out, state,
-                  state_stride, req_meta, slots, positions, H, Gq, dk, dv, vec_ok);
-    }
+#define LS_ONE(D, M) ls_walk_launch_one<PER, D, M>(grid, s, smem, q, k, v, ldq, ldk, ldv, gate, beta, head_decay, out, state, state_stride, req_meta, \
+                                                   slots, positions, H, Gq, dk, dv, vec_ok, chunk_gain)
+    if (mode == 1) LS_ONE(false, 1);
+    else if (mode == 2) LS_ONE(false, 2);
+    else if (delta) LS_ONE(true, 0);
+    else LS_ONE(false, 0);
+#undef LS_ONE
 }
 
 MM_EXPORT int mm_linear_state_walk(const void* q, const void* k, const void* v, int ldq, int ldk, int ldv, const void* gate,
@@ -426,9 +449,9 @@ MM_EXPORT int mm_linear_state_walk(const void* q, const void* k, const void* v, 
     const bool delta = beta != nullptr;
     const dim3 grid(ceil_div(dv, LS_COLS), H, n_requests);
     cudaStream_t s = (cudaStream_t)stream;
-#define LS_ARGS delta, grid, s, (const float*)q, (const float*)k, (const float*)v, ldq, ldk, ldv, (const float*)gate, (const float*)beta, \
+#define LS_ARGS delta, 0, grid, s, (const float*)q, (const float*)k, (const float*)v, ldq, ldk, ldv, (const float*)gate, (const float*)beta, \
                 (const float*)head_decay, (float*)out, (float*)state, state_stride, (const int32_t*)req_meta, (const int32_t*)slots,       \
-                (const int32_t*)positions, H, Gq, dk, dv
+                (const int32_t*)positions, H, Gq, dk, dv, (float*)nullptr
     if (dk <= 32) ls_walk_launch<4>(LS_ARGS);
     else if (dk <= 64) ls_walk_launch<8>(LS_ARGS);
     else if (dk <= 96) ls_walk_launch<12>(LS_ARGS);
@@ -436,5 +459,60 @@ MM_EXPORT int mm_linear_state_walk(const void* q, const void* k, const void* v, 
     else ls_walk_launch<32>(LS_ARGS);
 #undef LS_ARGS
     MM_CHECK_LAUNCH();
+    return MM_OK;
+}
+
+// The carry between the two chunk passes: thread per number of the state.  chunk_meta [chunks, 4] = (first token, tokens,
+// request, .), req_chunks [requests, 2] = (first chunk, chunks); scratch [chunks, H * dv * dk] holds what every chunk adds
+// and gets what every chunk starts from; gain [chunks, H].
+__global__ void linear_state_carry_kernel(float* __restrict__ scratch, const float* __restrict__ gain, float* __restrict__ state,
+                                          long long state_stride, const int32_t* __restrict__ chunk_meta, const int32_t* __restrict__ req_chunks,
+                                          const int32_t* __restrict__ slots, const int32_t* __restrict__ positions, int H, int per_head, long long size) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int r = blockIdx.y;
+    if (i >= size) return;
+    const int h = (int)(i / per_head);
+    const int first = req_chunks[2 * r], count = req_chunks[2 * r + 1];
+    float* st = state + (size_t)slots[r] * state_stride + i;
+    float S = positions[chunk_meta[4 * first]] == 0 ? 0.0f : *st;
+    for (int c = first; c < first + count; ++c) {
+        float* p = scratch + (size_t)c * size + i;
+        const float add = *p;
+        *p = S;
+        S = fmaf(gain[(size_t)c * H + h], S, add);
+    }
+    *st = S;
+}
+
+// Long portions without the delta rule, chunk by chunk (three launches).  scratch: fp32 [chunks, H * dv * dk], gain: fp32 [chunks, H].
+MM_EXPORT int mm_linear_state_chunked(const void* q, const void* k, const void* v, int ldq, int ldk, int ldv, const void* gate,
+                                      const void* head_decay, void* out, void* state, long long state_stride, const void* chunk_meta,
+                                      const void* req_chunks, const void* slots, const void* positions, int n_requests, int n_chunks, int H,
+                                      int Gq, int dk, int dv, void* scratch, void* gain, void* stream) {
+    MM_REQUIRE(H > 0 && Gq > 0 && H % Gq == 0 && dk > 0 && dv > 0 && dk <= 256, "linear state: heads must be a positive multiple of the q/k heads, keys at most 256");
+    MM_REQUIRE(gate != nullptr || head_decay != nullptr, "linear state: a decay per token or per head is needed");
+    MM_REQUIRE(state && slots && positions && chunk_meta && req_chunks && scratch && gain, "linear state: the chunked walk needs its lists and its scratch");
+    if (n_requests <= 0 || n_chunks <= 0) return MM_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long size = (long long)H * dv * dk;
+    const dim3 grid(ceil_div(dv, LS_COLS), H, n_chunks);
+    for (int mode = 1; mode <= 2; ++mode) {
+#define LS_ARGS false, mode, grid, s, (const float*)q, (const float*)k, (const float*)v, ldq, ldk, ldv, (const float*)gate, (const float*)nullptr, \
+                (const float*)head_decay, (float*)out, (float*)scratch, size, (const int32_t*)chunk_meta, (const int32_t*)slots,               \
+                (const int32_t*)positions, H, Gq, dk, dv, (float*)gain
+        if (dk <= 32) ls_walk_launch<4>(LS_ARGS);
+        else if (dk <= 64) ls_walk_launch<8>(LS_ARGS);
+        else if (dk <= 96) ls_walk_launch<12>(LS_ARGS);
+        else if (dk <= 128) ls_walk_launch<16>(LS_ARGS);
+        else ls_walk_launch<32>(LS_ARGS);
+#undef LS_ARGS
+        MM_CHECK_LAUNCH();
+        if (mode == 1) {
+            mm_launch(linear_state_carry_kernel, dim3(ceil_div(size, 256), n_requests), dim3(256), 0, s, (float*)scratch, (const float*)gain,
+                      (float*)state, state_stride, (const int32_t*)chunk_meta, (const int32_t*)req_chunks, (const int32_t*)slots,
+                      (const int32_t*)positions, H, dv * dk, size);
+            MM_CHECK_LAUNCH();
+        }
+    }
     return MM_OK;
 }

@@ -112,16 +112,51 @@ __global__ void moe_route_kernel(const float* __restrict__ z, int ldz, int n_tok
 // The router's product and its choice in one launch, one block per token: every warp takes experts in turn and sums
 // x . w_e over lanes in fp32 (a fixed order, whatever else is in the batch); then the first warp chooses.
 template <typename T>
-__global__ void __launch_bounds__(128) moe_router_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ w, int D, int E, int top,
-                                                         int groups, int keep, int32_t* __restrict__ idx, float* __restrict__ wts) {
+__device__ __forceinline__ void load8(const T* p, float* v);
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float* v) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float* v) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h[i]);
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) moe_router_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ w, int D, int E, int top,
+                                                         int groups, int keep, int vec, int32_t* __restrict__ idx, float* __restrict__ wts) {
     extern __shared__ float route_smem[];      // logits [E], scores [E], runs [groups]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const size_t t = blockIdx.x;
     const T* xr = x + t * ldx;
-    for (int e = warp; e < E; e += 4) {
+    for (int e = warp; e < E; e += 8) {
         const float* we = w + (size_t)e * D;
         float acc = 0.0f;
-        for (int d = lane; d < D; d += 32) acc = fmaf(to_f32<T>(xr[d]), we[d], acc);
+        if (vec) {        // rows that start on 16-byte boundaries: eight numbers per lane and step, several steps in flight
+            float a2 = 0.0f;
+#pragma unroll 4
+            for (int d = lane * 8; d < D; d += 256) {
+                float xv[8], wv[8];
+                load8<T>(xr + d, xv);
+                load8<float>(we + d, wv);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    acc = fmaf(xv[i], wv[i], acc);
+                    a2 = fmaf(xv[4 + i], wv[4 + i], a2);
+                }
+            }
+            acc += a2;
+        } else {
+            for (int d = lane; d < D; d += 32) acc = fmaf(to_f32<T>(xr[d]), we[d], acc);
+        }
         acc = warp_sum(acc);
         if (lane == 0) route_smem[e] = acc;
     }
@@ -136,12 +171,13 @@ MM_EXPORT int mm_moe_router(const void* x, int x_dtype, int ldx, const void* w, 
     MM_REQUIRE((size_t)(2 * E + groups) * sizeof(float) <= 48 * 1024, "moe router: too many experts for the router's shared memory");
     if (n_tokens == 0) return MM_OK;
     const size_t smem = (size_t)(2 * E + groups) * sizeof(float);
+    const int vec = D % 8 == 0 && ldx % 8 == 0 && (((uintptr_t)x | (uintptr_t)w) & 15) == 0;
     if (x_dtype == MM_F32)
-        mm_launch(moe_router_kernel<float>, dim3(n_tokens), dim3(128), smem, (cudaStream_t)stream, (const float*)x, ldx, (const float*)w, D, E, top,
-                  groups, keep, (int32_t*)idx, (float*)wts);
+        mm_launch(moe_router_kernel<float>, dim3(n_tokens), dim3(256), smem, (cudaStream_t)stream, (const float*)x, ldx, (const float*)w, D, E, top,
+                  groups, keep, vec, (int32_t*)idx, (float*)wts);
     else if (x_dtype == MM_BF16)
-        mm_launch(moe_router_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(128), smem, (cudaStream_t)stream, (const __nv_bfloat16*)x, ldx,
-                  (const float*)w, D, E, top, groups, keep, (int32_t*)idx, (float*)wts);
+        mm_launch(moe_router_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), smem, (cudaStream_t)stream, (const __nv_bfloat16*)x, ldx,
+                  (const float*)w, D, E, top, groups, keep, vec, (int32_t*)idx, (float*)wts);
     else
         MM_REQUIRE(false, "moe router: dtype must be float32 or bfloat16");
     MM_CHECK_LAUNCH();
@@ -168,6 +204,8 @@ MM_EXPORT int mm_moe_route(const void* z, int ldz, int n_tokens, int E, int top,
 // Also made here, for the grouped tensor-core products: the list of row tiles (first row, end row, expert; at most
 // `tile_rows` rows, none across an expert's border) with their number, each row's token (order / top), and each
 // (token, choice)'s place in the sorted order.
+#define SORT_FAST_EXPERTS 256
+
 __global__ void moe_sort_kernel(const int32_t* __restrict__ idx, int n_rows, int E, int32_t* __restrict__ offsets, int32_t* __restrict__ order,
                                 int top, int tile_rows, int32_t* __restrict__ tiles, int32_t* __restrict__ n_tiles,
                                 int32_t* __restrict__ row_token, int32_t* __restrict__ place) {
@@ -198,13 +236,57 @@ __global__ void moe_sort_kernel(const int32_t* __restrict__ idx, int n_rows, int
         }
     }
     __syncthreads();
-    // stable placement: the rows are taken in rounds of blockDim.x; inside a round a row's rank among the rows of its
-    // expert is counted by ballot within the warp and by a pass over the warps in order
+    // stable placement
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    auto put = [&](int r, int at) {
+        order[at] = r;
+        if (row_token != nullptr) row_token[at] = r / top;
+        if (place != nullptr) place[r] = at;
+    };
+    if (E <= SORT_FAST_EXPERTS) {
+        // every warp owns a run of consecutive rows: it counts its rows per expert, the counts of the warps before it give
+        // its first place in every expert's list, and it then places its rows 32 at a time (a row's rank among the rows
+        // of its expert inside the 32 comes from a match over the warp)
+        int32_t* wcount = cursor + E;                              // [warps][E]
+        const int per_warp = (n_rows + warps - 1) / warps;
+        const int lo = min(n_rows, warp * per_warp), hi = min(n_rows, lo + per_warp);
+        for (int e = lane; e < E; e += 32) wcount[warp * E + e] = 0;
+        __syncwarp();
+        for (int r = lo + lane; r < hi; r += 32) atomicAdd(&wcount[warp * E + idx[r]], 1);
+        __syncthreads();
+        for (int e = threadIdx.x; e < E; e += blockDim.x) {
+            int at = offsets[e];
+            for (int w = 0; w < warps; ++w) {
+                const int c = wcount[w * E + e];
+                wcount[w * E + e] = at;
+                at += c;
+            }
+        }
+        __syncthreads();
+        for (int base = lo; base < hi; base += 32) {
+            const int r = base + lane;
+            const int e = r < hi ? idx[r] : -1;
+            if (e >= 0) {
+                const unsigned peers = __match_any_sync(__activemask(), e);
+                const int rank = __popc(peers & ((1u << lane) - 1));
+                const int first = __ffs(peers) - 1;
+                int start = 0;
+                if (lane == first) {
+                    start = wcount[warp * E + e];
+                    wcount[warp * E + e] = start + __popc(peers);
+                }
+                start = __shfl_sync(peers, start, first);
+                put(r, start + rank);
+            }
+            __syncwarp();
+        }
+        return;
+    }
+    // many experts: the rows are taken in rounds of blockDim.x, and the warps of a round take their turn
     for (int base = 0; base < n_rows; base += blockDim.x) {
         const int r = base + threadIdx.x;
         const int e = r < n_rows ? idx[r] : -1;
-        for (int w = 0; w < warps; ++w) {           // warps take their turn: the cursor moves in row order
+        for (int w = 0; w < warps; ++w) {
             if (w == warp && e >= 0) {
                 const unsigned peers = __match_any_sync(__activemask(), e);
                 const int rank = __popc(peers & ((1u << lane) - 1));
@@ -212,9 +294,7 @@ __global__ void moe_sort_kernel(const int32_t* __restrict__ idx, int n_rows, int
                 int start = 0;
                 if (lane == first) start = atomicAdd(&cursor[e], __popc(peers));
                 start = __shfl_sync(peers, start, first);
-                order[start + rank] = r;
-                if (row_token != nullptr) row_token[start + rank] = r / top;
-                if (place != nullptr) place[r] = start + rank;
+                put(r, start + rank);
             }
             __syncthreads();
         }
@@ -225,7 +305,9 @@ MM_EXPORT int mm_moe_sort(const void* idx, int n_rows, int E, void* offsets, voi
                           void* row_token, void* place, void* stream) {
     MM_REQUIRE(n_rows >= 0 && E > 0 && E <= 4096 && top > 0, "moe sort: bad sizes");
     MM_REQUIRE(tiles == nullptr || (tile_rows > 0 && n_tiles != nullptr), "moe sort: the tile list needs its tile size and its count");
-    mm_launch(moe_sort_kernel, dim3(1), dim3(n_rows > 256 ? 1024 : 256), (size_t)2 * E * sizeof(int32_t), (cudaStream_t)stream,
+    const int threads = n_rows > 256 ? 1024 : 256;
+    const size_t sort_smem = (size_t)(2 + (E <= SORT_FAST_EXPERTS ? threads / 32 : 0)) * E * sizeof(int32_t);
+    mm_launch(moe_sort_kernel, dim3(1), dim3(threads), sort_smem, (cudaStream_t)stream,
               (const int32_t*)idx, n_rows, E, (int32_t*)offsets, (int32_t*)order, top, tile_rows, (int32_t*)tiles, (int32_t*)n_tiles,
               (int32_t*)row_token, (int32_t*)place);
     MM_CHECK_LAUNCH();

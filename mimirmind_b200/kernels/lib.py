@@ -69,6 +69,7 @@ _PROTOTYPES = {
     "mm_moe_router": [P, I, I, P, I, I, I, I, I, I, P, P, P],
     "mm_angle_table": [P, P, P, I, I, P],
     "mm_linear_state_walk": [P, P, P, I, I, I, P, P, P, P, P, c_longlong, P, P, P, I, I, I, I, I, P],
+    "mm_linear_state_chunked": [P, P, P, I, I, I, P, P, P, P, c_longlong, P, P, P, P, I, I, I, I, I, I, P, P, P],
     "mm_gated_group_norm": [P, I, I, P, I, I, P, I, P, I, I, I, I, F, I, I, P],
     "mm_normed_mean2": [P, P, P, P, P, I, I, I, F, F, P],
     "mm_moe_route": [P, I, I, I, I, I, I, P, P, P],

@@ -997,6 +997,39 @@ def linear_state_walk(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: 
     return out
 
 
+def linear_state_chunked(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, chunk_meta: torch.Tensor, req_chunks: torch.Tensor,
+                         slots: torch.Tensor, positions: torch.Tensor, heads: int, qk_heads: int, dk: int, dv: int,
+                         gate: Optional[torch.Tensor] = None, head_decay: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The same recurrence without the delta rule for long portions, chunk by chunk (three launches: every chunk from a zero
+    state, the carry along each request's chunks, every chunk again from its starting state).  ``chunk_meta`` [chunks, 4] =
+    (first token, tokens, request, .), ``req_chunks`` [requests, 2] = (first chunk, chunks)."""
+    for t, what in ((q, "q"), (k, "k"), (v, "v")):
+        if t.dtype != torch.float32 or not t.is_cuda or t.stride(1) != 1:
+            raise KernelError(f"linear state {what}: fp32 rows with unit column stride are needed")
+    n = q.shape[0]
+    if q.shape[1] != qk_heads * dk or k.shape != q.shape or v.shape != (n, heads * dv):
+        raise KernelError("linear state: shape mismatch")
+    if state.dtype != torch.float32 or state.stride(-1) != 1 or state.shape[1] < heads * dv * dk:
+        raise KernelError("linear state: the state is fp32 [slots, >= heads * dv * dk]")
+    _need(chunk_meta, "chunk_meta", torch.int32)
+    _need(req_chunks, "req_chunks", torch.int32)
+    _need(slots, "state slots", torch.int32)
+    _need(positions, "positions", torch.int32)
+    if gate is not None:
+        _need(gate, "gate", torch.float32)
+    if head_decay is not None:
+        _need(head_decay, "head decay", torch.float32)
+    n_chunks, n_req = chunk_meta.shape[0], req_chunks.shape[0]
+    out = torch.empty((n, heads * dv), dtype=torch.float32, device=q.device)
+    scratch = torch.empty((max(1, n_chunks), heads * dv * dk), dtype=torch.float32, device=q.device)
+    gain = torch.empty((max(1, n_chunks), heads), dtype=torch.float32, device=q.device)
+    check(_lib.load().mm_linear_state_chunked(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), k.stride(0), v.stride(0), _ptr(gate),
+                                              _ptr(head_decay), out.data_ptr(), state.data_ptr(), state.stride(0), chunk_meta.data_ptr(),
+                                              req_chunks.data_ptr(), slots.data_ptr(), positions.data_ptr(), n_req, n_chunks, heads, qk_heads,
+                                              dk, dv, scratch.data_ptr(), gain.data_ptr(), _stream()), "linear_state_chunked")
+    return out
+
+
 GATE_ACTIVATIONS = {"silu": 1, "sigmoid": 2}
 
 

@@ -33,9 +33,12 @@ from ..config.spec import PartSpec, TensorSpec
 from ..kernels import ops
 from ..registry import MIXERS
 from .base import LayerCache, Mixer, Runtime, StateSpec, StepContext, WeightView
+from .chunks import token_chunks
 from .linear import linear
 
 
+CHUNK = 64                   # tokens per chunk of the three-pass walk
+CHUNKED_FROM = 256           # a step whose longest portion has at least this many tokens walks its chunks side by side (not in float32)
 CONV_BY_TOKEN_FROM = 32      # a step whose longest portion has at least this many tokens runs the convolution per (token, channel)
 
 
@@ -153,9 +156,16 @@ class LinearStateMixer(Mixer):
             rot_dims=self.rot_dims, unit=self.unit_eps is not None, unit_eps=float(self.unit_eps or 0.0), q_scale=self.q_scale,
             k_scale=self.k_scale, a_off=self.a_off if self.learned_decay else -1, b_off=self.b_off, heads=H, A_log=self.A_log,
             dt_bias=self.dt_bias, gate_rows=gate_rows)
-        o = ops.linear_state_walk(qkv[:, self.q_off:self.q_off + G * dk], qkv[:, self.k_off:self.k_off + G * dk], qkv[:, self.v_off:self.v_off + H * dv],
-                                  state, ctx.req_meta, ctx.state_slots, ctx.positions, ctx.n_requests, H, G, dk, dv,
-                                  gate=gate, beta=beta, head_decay=self.head_decay)
+        qs, ks_, vs = qkv[:, self.q_off:self.q_off + G * dk], qkv[:, self.k_off:self.k_off + G * dk], qkv[:, self.v_off:self.v_off + H * dv]
+        # the 32-bit path keeps one order of operations whatever the cutting: it always walks; so does the delta rule,
+        # whose update of the state is not a scaling and an addition
+        if not self.delta and ctx.max_q_len >= CHUNKED_FROM and self.rt.dtype != torch.float32:
+            chunk_meta, req_chunks = token_chunks(ctx, CHUNK)
+            o = ops.linear_state_chunked(qs, ks_, vs, state, chunk_meta, req_chunks, ctx.state_slots, ctx.positions, H, G, dk, dv,
+                                         gate=gate, head_decay=self.head_decay)
+        else:
+            o = ops.linear_state_walk(qs, ks_, vs, state, ctx.req_meta, ctx.state_slots, ctx.positions, ctx.n_requests, H, G, dk, dv,
+                                      gate=gate, beta=beta, head_decay=self.head_decay)
         g = a[:, self.g_off:self.g_off + H * dv]
         if self.out_norm == "head":
             y = ops.gated_group_norm(o, H, dv, self.rt.dtype, eps=self.eps, weight=self.out_weight, gate=g, activation=self.gate_activation)

@@ -9,13 +9,13 @@ from __future__ import annotations
 
 from typing import List, Optional
 
-import numpy as np
 import torch
 
 from ..config.spec import PartSpec, TensorSpec
 from ..kernels import ops
 from ..registry import MIXERS
 from .base import LayerCache, Mixer, Runtime, StateSpec, StepContext, WeightView
+from .chunks import token_chunks
 from .linear import linear
 
 CHUNK = 64               # tokens per chunk of the three-pass scan
@@ -50,23 +50,8 @@ class MinGRU(Mixer):
 
     @staticmethod
     def _chunks(ctx: StepContext):
-        """The step's tokens cut into chunks, per request in order: (chunk_meta [chunks, 4], req_chunks [requests, 2])
-        on the device, made once per step."""
-        key = ("mingru_chunks", CHUNK)
-        if key not in ctx.derived:
-            meta, per_req = [], []
-            for r, (s, n) in enumerate(zip(ctx.q_start, ctx.q_len)):
-                first = len(meta)
-                for off in range(0, n, CHUNK):
-                    meta.append((s + off, min(CHUNK, n - off), r, int(off == 0)))
-                per_req.append((first, len(meta) - first))
-            host = np.concatenate([np.asarray(meta, dtype=np.int32).reshape(-1), np.asarray(per_req, dtype=np.int32).reshape(-1)])
-            # from pinned memory, without waiting for the device (a pageable copy would stall the launches behind it)
-            pinned = torch.from_numpy(host).pin_memory()
-            dev = pinned.to(ctx.token_ids.device, non_blocking=True)
-            ctx.derived[key] = (dev[:4 * len(meta)].view(len(meta), 4), dev[4 * len(meta):].view(len(per_req), 2))
-            ctx.derived[key + ("staged",)] = pinned
-        return ctx.derived[key]
+        """The step's tokens cut into chunks, per request in order, made once per step."""
+        return token_chunks(ctx, CHUNK)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
         n = x.shape[0]

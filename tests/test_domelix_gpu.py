@@ -117,6 +117,44 @@ def test_a_constant_decay_per_head_and_long_walks():
         assert torch.equal(one[0].cpu(), torch.from_numpy(whole[t])), t
 
 
+@pytest.mark.parametrize("H,G,dk,dv,per_token", [(3, 3, 24, 16, False), (4, 2, 64, 40, True), (2, 2, 128, 128, False), (2, 1, 10, 7, True)])
+def test_chunks_walked_side_by_side_equal_the_walk(H, G, dk, dv, per_token):
+    """Long portions without the delta rule: every chunk from zero, the carry, every chunk from its starting state.  Three
+    requests (one of a single partial chunk, one that goes on from an earlier state, one starting at position 0 in a slot
+    somebody left full) against the plain recurrence, with a constant decay per head and with one per token."""
+    from mimirmind_b200.kernels import ops
+    rng = np.random.RandomState(dk + dv)
+    lens, starts, slots = [300, 37, 129], [0, 50, 0], [1, 3, 0]
+    size = H * dv * dk
+    state = torch.full((4, size + 2), 3.0, dtype=torch.float32, device=DEV)
+    earlier = rng.randn(H, dk, dv)
+    state[3, :size] = dev(earlier.transpose(0, 2, 1).reshape(-1))
+    n = sum(lens)
+    q, k, v = rng.randn(n, G, dk) / math.sqrt(dk), rng.randn(n, G, dk) / math.sqrt(dk), rng.randn(n, H, dv)
+    head_decay = rng.uniform(0.8, 1.0, size=H)
+    decay = rng.uniform(0.8, 1.0, size=(n, H)) if per_token else np.tile(head_decay, (n, 1))
+    meta, req_chunks, pos, at = [], [], [], 0
+    for r, ln in enumerate(lens):
+        first = len(meta)
+        for off in range(0, ln, 64):
+            meta.append([at + off, min(64, ln - off), r, int(off == 0)])
+        req_chunks.append([first, len(meta) - first])
+        pos += list(range(starts[r], starts[r] + ln))
+        at += ln
+    got = ops.linear_state_chunked(dev(q.reshape(n, -1)), dev(k.reshape(n, -1)), dev(v.reshape(n, -1)), state, i32(meta), i32(req_chunks), i32(slots),
+                                   i32(pos), H, G, dk, dv, gate=dev(decay) if per_token else None,
+                                   head_decay=None if per_token else dev(head_decay)).cpu().numpy().reshape(n, H, dv)
+    at = 0
+    for r, ln in enumerate(lens):
+        sl = slice(at, at + ln)
+        want, S = state_mixer_reference(q[sl], k[sl], v[sl], decay[sl], None, earlier if r == 1 else None)
+        assert np.abs(got[sl] - want).max() <= 5e-5 * max(1.0, np.abs(want).max()), f"request {r}"
+        kept = state[slots[r], :size].cpu().numpy().reshape(H, dv, dk)
+        assert np.abs(kept - S.transpose(0, 2, 1)).max() <= 5e-5 * max(1.0, np.abs(S).max()), f"state of request {r}"
+        at += ln
+    assert (state[2] == 3.0).all() and (state[:, size:] == 3.0).all()
+
+
 @pytest.mark.parametrize("by_token", [False, True])
 @pytest.mark.parametrize("taps", [1, 2, 4, 8])
 def test_the_short_convolution_carries_its_last_inputs(taps, by_token):
