@@ -78,6 +78,8 @@ class LinearStateMixer(Mixer):
         if dk > 256:
             raise ValueError("linear state: key sizes above 256 are not supported")
         self.taps = int(spec.get("conv", 0) or 0)
+        if self.taps > 8:
+            raise ValueError("linear state: convolutions of more than 8 taps are not supported")
         self.activation = spec.get("activation")
         if self.activation not in (None, "silu"):
             raise ValueError("linear state: the activation is 'silu' or None")

@@ -63,8 +63,13 @@ CONFIGS = {
         delta(1, 1, 12, 6, 1),
         parallel((6, 2, 10, 12, 0.3, 130, 16), (5, 6, 3, (0.2, 0.6, 0.9, 0.99, 0.999))),
     ]),
+    # no layer keeps keys and values (no page pool at all), a single layer of each remaining kind, one expert of one
+    "N": config(90, 48, 1e-5, [
+        retention(2, 16, 8, (0.9, 0.99), rot=(16, 50.0), mlp=moe(16, 1, 1)),
+        delta(2, 1, 8, 16, 4, moe(16, 3, 2)),
+    ]),
 }
-LENGTHS = {"P": [1, 9, 77, 300], "Q": [5, 70, 280], "R": [2, 33, 150, 270]}
+LENGTHS = {"P": [1, 9, 77, 300], "Q": [5, 70, 280], "R": [2, 33, 150, 270], "N": [3, 40, 290]}
 
 
 def tensor_shapes(cfg):

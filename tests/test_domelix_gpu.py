@@ -471,7 +471,7 @@ def check_rows(trace, outputs, reqs, ref, dtype, what):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name,page_size", [("P", 16), ("Q", 16), ("R", 8), ("P", 32)])
+@pytest.mark.parametrize("name,page_size", [("P", 16), ("Q", 16), ("R", 8), ("P", 32), ("N", 16)])
 def test_every_way_of_cutting_matches_the_plain_implementation(name, page_size, dtype, models):
     folder, cfg, w = models(name)
     reqs = {f"{name}{i}": random_tokens(cfg["vocab"], n, 100 * i + n) for i, n in enumerate(du.LENGTHS[name])}
@@ -500,7 +500,7 @@ def test_every_way_of_cutting_matches_the_plain_implementation(name, page_size, 
     ref2 = dict(ref)
     ref2.update({rid + "x": ref[rid] for rid in reqs})
     results["mixed"] = check_rows(t, out, twice, ref2, dtype, "mixed")
-    assert runner.manager.reuses() > 0, "the pool was large enough that no page was used again"
+    assert runner.manager.reuses() > 0 or not runner.manager.groups, "the pool was large enough that no page was used again"
     for g in runner.manager.groups:
         assert runner.manager.free_pages(g) == runner.manager.total_pages(g)
     if dtype == "float32":
