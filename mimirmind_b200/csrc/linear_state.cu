@@ -148,35 +148,36 @@ __global__ void linear_state_prep_kernel(float* __restrict__ x, int ld, int q_of
                                          float q_scale, float k_scale, const float* __restrict__ gx, int gld, int a_off, int b_off, int H,
                                          const float* __restrict__ A_log, const float* __restrict__ dt_bias, float* __restrict__ gate,
                                          float* __restrict__ beta) {
+    extern __shared__ float prep_smem[];             // one vector of dk per warp: a head is read once and written once
     const int t = blockIdx.x;
     float* row = x + (size_t)t * ld;
     const float* grow = gx + (size_t)t * gld;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     const int half = rot_dims / 2;
+    float* sv = prep_smem + warp * dk;
     for (int vec = warp; vec < 2 * Gq; vec += warps) {
         const bool is_q = vec < Gq;
         float* p = row + (is_q ? q_off + vec * dk : k_off + (vec - Gq) * dk);
-        if (act)
-            for (int d = lane; d < dk; d += 32) p[d] = ls_silu(p[d]);
+        for (int d = lane; d < dk; d += 32) sv[d] = act ? ls_silu(p[d]) : p[d];
         __syncwarp();
         if (rot_dims) {
             const float2* cs = rot + (size_t)t * half;
             for (int i = lane; i < half; i += 32) {
-                const float a = p[i], b = p[i + half];
-                p[i] = a * cs[i].x - b * cs[i].y;
-                p[i + half] = b * cs[i].x + a * cs[i].y;
+                const float a = sv[i], b = sv[i + half];
+                sv[i] = a * cs[i].x - b * cs[i].y;
+                sv[i + half] = b * cs[i].x + a * cs[i].y;
             }
             __syncwarp();
         }
         float f = is_q ? q_scale : k_scale;
         if (unit) {
             float ss = 0.0f;
-            for (int d = lane; d < dk; d += 32) ss = fmaf(p[d], p[d], ss);
+            for (int d = lane; d < dk; d += 32) ss = fmaf(sv[d], sv[d], ss);
             ss = warp_sum(ss);
             f *= 1.0f / sqrtf(ss + unit_eps);
         }
-        if (f != 1.0f)
-            for (int d = lane; d < dk; d += 32) p[d] *= f;
+        for (int d = lane; d < dk; d += 32) p[d] = f != 1.0f ? sv[d] * f : sv[d];
+        __syncwarp();
     }
     if (act)
         for (int d = threadIdx.x; d < n_v; d += blockDim.x) row[v_off + d] = ls_silu(row[v_off + d]);
@@ -200,7 +201,8 @@ MM_EXPORT int mm_linear_state_prep(void* x, int ld, int n_tokens, int q_off, int
     MM_REQUIRE(b_off < 0 || (H > 0 && beta), "linear state prep: the write strength needs its output");
     if (a_off < 0 && b_off < 0) H = 0;
     if (n_tokens == 0) return MM_OK;
-    mm_launch(linear_state_prep_kernel, dim3(n_tokens), dim3(128), 0, (cudaStream_t)stream, (float*)x, ld, q_off, k_off, v_off, Gq, dk, n_v, act,
+    MM_REQUIRE(dk <= 1024, "linear state prep: key sizes above 1024 are not supported");
+    mm_launch(linear_state_prep_kernel, dim3(n_tokens), dim3(256), (size_t)8 * dk * sizeof(float), (cudaStream_t)stream, (float*)x, ld, q_off, k_off, v_off, Gq, dk, n_v, act,
               (const float2*)rot, rot_dims, unit, unit_eps, q_scale, k_scale, (const float*)gx, gld, a_off, b_off, H, (const float*)A_log,
               (const float*)dt_bias,
               (float*)gate, (float*)beta);

@@ -339,6 +339,8 @@ __device__ __forceinline__ bool moe_tile(const int32_t* __restrict__ offsets, in
 #define MOE_BM 64
 #define MOE_BN 64
 #define MOE_BK 16
+#define MOE_MMA_BK 64
+#define MOE_STAGES 3
 
 // fp32 FMA units, every output summed over k in ascending order.  GATED: W is [E, 2F, K], the gate's rows then the
 // up rows, and the output is act(gate) * up over F columns, the input rows gathered through order / top; otherwise
@@ -433,14 +435,21 @@ __global__ void __launch_bounds__(256) moe_gemm_simt_kernel(const TA* __restrict
 }
 
 // bfloat16 on the tensor cores (mma.sync m16n8k16, fp32 accumulation): the same tiles, 64 rows x 64 columns, four
-// warps of 32 x 32 (gated: gate and up accumulators side by side), K in steps of 32 through shared memory.
+// warps of 32 x 32 (gated: gate and up accumulators side by side), K in steps of 64 through a ring of shared-memory stages.
 template <bool GATED, typename TC>
 __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ W,
                                                            TC* __restrict__ C, int ldc, const int32_t* __restrict__ offsets,
                                                            const int32_t* __restrict__ order, int E, int top, int N, int K, int interleaved) {
-    constexpr int BK = 32, LD = BK + 8;      // 80-byte rows: ldmatrix reads without bank conflicts
-    __shared__ __align__(16) __nv_bfloat16 As[2][MOE_BM][LD];
-    __shared__ __align__(16) __nv_bfloat16 Ws[2][GATED ? 2 * MOE_BN : MOE_BN][LD];
+    // K in steps of 64 through a ring of MOE_STAGES stages: a decode step's tiles hold a handful of rows and stream a
+    // whole expert, so what counts is how many bytes of weights a CTA keeps in flight (rows of 144 bytes: ldmatrix
+    // reads without bank conflicts)
+    constexpr int BK = MOE_MMA_BK, LD = BK + 8;
+    constexpr int WROWS_ = GATED ? 2 * MOE_BN : MOE_BN;
+    extern __shared__ __align__(16) unsigned char moe_smem[];
+    typedef __nv_bfloat16 (*ATile)[MOE_BM][LD];
+    typedef __nv_bfloat16 (*WTile)[WROWS_][LD];
+    ATile As = reinterpret_cast<ATile>(moe_smem);
+    WTile Ws = reinterpret_cast<WTile>(moe_smem + sizeof(__nv_bfloat16) * MOE_STAGES * MOE_BM * LD);
     __shared__ int32_t rows[MOE_BM];
     __shared__ int tile_info[3];
     const int tid = threadIdx.x;
@@ -473,15 +482,15 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const __nv_bfloat16* 
                 if (GATED) up[a][b][c] = 0.0f;
             }
     auto load = [&](int stage, int k0) {
-        // 16-byte chunks: 4 per row of 32 k
-        for (int i = tid; i < MOE_BM * 4; i += 128) {
-            const int r = i >> 2, c = (i & 3) * 8;
+        // 16-byte chunks: 8 per row of 64 k
+        for (int i = tid; i < MOE_BM * 8; i += 128) {
+            const int r = i >> 3, c = (i & 7) * 8;
             __nv_bfloat16* dst = &As[stage][r][c];
             if (rows[r] >= 0 && k0 + c < K) cp_async16(dst, A + (size_t)rows[r] * lda + k0 + c);
             else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
         }
-        for (int i = tid; i < WROWS * 4; i += 128) {
-            const int r = i >> 2, c = (i & 3) * 8;
+        for (int i = tid; i < WROWS * 8; i += 128) {
+            const int r = i >> 3, c = (i & 7) * 8;
             // gated: column j of the gate is row j of the expert's matrix and the up column row N + j, or, interleaved in
             // blocks of 8 (the layout the tensor-memory product's epilogue wants), rows 16 (j / 8) + j % 8 and + 8
             const int j = GATED ? (r < MOE_BN ? n0 + r : n0 + r - MOE_BN) : n0 + r;
@@ -494,16 +503,17 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const __nv_bfloat16* 
         cp_async_commit();
     };
     const int steps = (K + BK - 1) / BK;
-    load(0, 0);
+#pragma unroll
+    for (int p = 0; p < MOE_STAGES - 1; ++p) {
+        if (p < steps) load(p, p * BK);
+        else cp_async_commit();              // an empty group keeps the count of groups in step
+    }
     for (int s = 0; s < steps; ++s) {
-        if (s + 1 < steps) {
-            load((s + 1) & 1, (s + 1) * BK);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncthreads();
-        const int st = s & 1;
+        cp_async_wait<MOE_STAGES - 2>();     // the copies of step s have landed
+        __syncthreads();                     // ... for every thread, and the stage of step s - 1 is free
+        if (s + MOE_STAGES - 1 < steps) load((s + MOE_STAGES - 1) % MOE_STAGES, (s + MOE_STAGES - 1) * BK);
+        else cp_async_commit();
+        const int st = s % MOE_STAGES;
 #pragma unroll
         for (int kk = 0; kk < BK; kk += 16) {
             uint32_t af[2][4];
@@ -530,7 +540,6 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const __nv_bfloat16* 
                 }
             }
         }
-        __syncthreads();
     }
 #pragma unroll
     for (int mi = 0; mi < 2; ++mi)
@@ -566,12 +575,20 @@ MM_EXPORT int mm_moe_gemm(const void* A, int a_dtype, int lda, const void* W, in
     const int32_t* off = (const int32_t*)offsets;
     const int32_t* ord = (const int32_t*)order;
     if (tensor_cores && a_dtype == MM_BF16 && w_dtype == MM_BF16 && K % 8 == 0 && lda % 8 == 0 && ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0) {
+        const size_t tile_smem = sizeof(bf) * MOE_STAGES * (MOE_BM + (gated ? 2 : 1) * MOE_BN) * (MOE_MMA_BK + 8);
+        static bool configured = false;
+        if (!configured) {
+            cudaFuncSetAttribute(moe_gemm_mma_kernel<true, bf>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(sizeof(bf) * MOE_STAGES * (MOE_BM + 2 * MOE_BN) * (MOE_MMA_BK + 8)));
+            cudaFuncSetAttribute(moe_gemm_mma_kernel<false, bf>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(sizeof(bf) * MOE_STAGES * (MOE_BM + MOE_BN) * (MOE_MMA_BK + 8)));
+            cudaFuncSetAttribute(moe_gemm_mma_kernel<false, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(sizeof(bf) * MOE_STAGES * (MOE_BM + MOE_BN) * (MOE_MMA_BK + 8)));
+            configured = true;
+        }
         if (gated && c_dtype == MM_BF16)
-            mm_launch(moe_gemm_mma_kernel<true, bf>, grid, dim3(128), 0, s, (const bf*)A, lda, (const bf*)W, (bf*)C, ldc, off, ord, E, top, N, K, interleaved);
+            mm_launch(moe_gemm_mma_kernel<true, bf>, grid, dim3(128), tile_smem, s, (const bf*)A, lda, (const bf*)W, (bf*)C, ldc, off, ord, E, top, N, K, interleaved);
         else if (!gated && c_dtype == MM_BF16)
-            mm_launch(moe_gemm_mma_kernel<false, bf>, grid, dim3(128), 0, s, (const bf*)A, lda, (const bf*)W, (bf*)C, ldc, off, ord, E, top, N, K, 0);
+            mm_launch(moe_gemm_mma_kernel<false, bf>, grid, dim3(128), tile_smem, s, (const bf*)A, lda, (const bf*)W, (bf*)C, ldc, off, ord, E, top, N, K, 0);
         else if (!gated && c_dtype == MM_F32)
-            mm_launch(moe_gemm_mma_kernel<false, float>, grid, dim3(128), 0, s, (const bf*)A, lda, (const bf*)W, (float*)C, ldc, off, ord, E, top, N, K, 0);
+            mm_launch(moe_gemm_mma_kernel<false, float>, grid, dim3(128), tile_smem, s, (const bf*)A, lda, (const bf*)W, (float*)C, ldc, off, ord, E, top, N, K, 0);
         else
             MM_REQUIRE(false, "moe gemm: this combination of dtypes is not built");
         MM_CHECK_LAUNCH();

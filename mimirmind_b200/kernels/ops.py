@@ -1152,10 +1152,6 @@ def moe_gemm(a: torch.Tensor, w: torch.Tensor, rows: ExpertRows, n_rows: int, to
     return out
 
 
-def moe_gemm_grouped_supported(n_rows: int, n: int, k: int) -> bool:
-    return n_rows > 0 and k % 8 == 0 and n % 16 == 0
-
-
 def moe_gemm_grouped(a: torch.Tensor, w: torch.Tensor, rows: ExpertRows, swiglu: bool) -> torch.Tensor:
     """The grouped tensor-memory product: ``a`` [n_rows, K] bf16 in sorted order, ``w`` [E, N, K] bf16; every row tile of
     ``rows.tiles`` times its expert's matrix.  ``swiglu``: the matrix interleaves gate and up rows in blocks of 8 and the
