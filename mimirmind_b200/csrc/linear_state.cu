@@ -270,6 +270,7 @@ __global__ void __launch_bounds__(128) linear_state_walk_kernel(
     constexpr int ROUND = LS_AHEAD * (2 * DKP + LS_COLS + 2);      // floats of one buffer: q, k, v, decay, write strength
     extern __shared__ __align__(16) float ls_smem[];
     float* so = ls_smem + 2 * ROUND;                               // [AHEAD][COLS]
+    float* skq = so + LS_AHEAD * LS_COLS;                          // [AHEAD] k . q of the round's tokens
 
     const int h = blockIdx.y, r = blockIdx.z;
     const int col0 = blockIdx.x * LS_COLS;
@@ -354,33 +355,40 @@ __global__ void __launch_bounds__(128) linear_state_walk_kernel(
         const float* sv = sk + LS_AHEAD * DKP;
         const float* sg = sv + LS_AHEAD * LS_COLS;
         const float* sb = sg + LS_AHEAD;
+        if (MODE != 1) {
+            // k . q of every token of the round, once for all columns: a warp takes every fourth token
+            for (int tt = warp; tt < cnt; tt += 4) {
+                float d = 0.0f;
+                for (int i = lane; i < DKP; i += 32) d = fmaf(sk[tt * DKP + i], sq[tt * DKP + i], d);
+                d = warp_sum(d);
+                if (lane == 0) skq[tt] = d;
+            }
+            __syncthreads();
+        }
 #pragma unroll 4
         for (int tt = 0; tt < cnt; ++tt) {
             const float4* q4 = reinterpret_cast<const float4*>(sq + tt * DKP) + ks;
             const float4* k4 = reinterpret_cast<const float4*>(sk + tt * DKP) + ks;
             float kk[PER];
-            float dq[4] = {0.0f, 0.0f, 0.0f, 0.0f}, dkk[4] = {0.0f, 0.0f, 0.0f, 0.0f}, kq[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            float dq[4] = {0.0f, 0.0f, 0.0f, 0.0f}, dkk[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int j = 0; j < PER / 4; ++j) {
                 const float4 qv = q4[j * 8], kv = k4[j * 8];
                 kk[4 * j] = kv.x; kk[4 * j + 1] = kv.y; kk[4 * j + 2] = kv.z; kk[4 * j + 3] = kv.w;
                 dq[0] = fmaf(S[4 * j], qv.x, dq[0]); dq[1] = fmaf(S[4 * j + 1], qv.y, dq[1]);
                 dq[2] = fmaf(S[4 * j + 2], qv.z, dq[2]); dq[3] = fmaf(S[4 * j + 3], qv.w, dq[3]);
-                kq[0] = fmaf(kv.x, qv.x, kq[0]); kq[1] = fmaf(kv.y, qv.y, kq[1]);
-                kq[2] = fmaf(kv.z, qv.z, kq[2]); kq[3] = fmaf(kv.w, qv.w, kq[3]);
                 if (DELTA) {
                     dkk[0] = fmaf(S[4 * j], kv.x, dkk[0]); dkk[1] = fmaf(S[4 * j + 1], kv.y, dkk[1]);
                     dkk[2] = fmaf(S[4 * j + 2], kv.z, dkk[2]); dkk[3] = fmaf(S[4 * j + 3], kv.w, dkk[3]);
                 }
             }
-            float sdq = (dq[0] + dq[1]) + (dq[2] + dq[3]), skq = (kq[0] + kq[1]) + (kq[2] + kq[3]);
+            float sdq = (dq[0] + dq[1]) + (dq[2] + dq[3]);
             float sdk = DELTA ? (dkk[0] + dkk[1]) + (dkk[2] + dkk[3]) : 0.0f;
             if (MODE != 1) {
 #pragma unroll
                 for (int o = 1; o < 8; o <<= 1) {
                     if (DELTA) sdk += __shfl_xor_sync(0xffffffffu, sdk, o);
                     sdq += __shfl_xor_sync(0xffffffffu, sdq, o);
-                    skq += __shfl_xor_sync(0xffffffffu, skq, o);
                 }
             }
             const float g = sg[tt];
@@ -389,7 +397,7 @@ __global__ void __launch_bounds__(128) linear_state_walk_kernel(
 #pragma unroll
             for (int e = 0; e < PER; ++e) S[e] = fmaf(kk[e], u, g * S[e]);
             if (MODE == 1) gain *= g;
-            if (MODE != 1 && ks == 0) so[tt * LS_COLS + cl] = fmaf(u, skq, g * sdq);     // S_new^T q = g S_old^T q + u (k . q)
+            if (MODE != 1 && ks == 0) so[tt * LS_COLS + cl] = fmaf(u, skq[tt], g * sdq);     // S_new^T q = g S_old^T q + u (k . q)
         }
         __syncthreads();
         if (MODE != 1)
@@ -426,7 +434,7 @@ static void ls_walk_launch(bool delta, int mode, dim3 grid, cudaStream_t s, cons
                            const float* gate, const float* beta, const float* head_decay, float* out, float* state, long long state_stride,
                            const int32_t* req_meta, const int32_t* slots, const int32_t* positions, int H, int Gq, int dk, int dv,
                            float* chunk_gain) {
-    const size_t smem = sizeof(float) * (2 * LS_AHEAD * (2 * 8 * PER + LS_COLS + 2) + LS_AHEAD * LS_COLS);
+    const size_t smem = sizeof(float) * (2 * LS_AHEAD * (2 * 8 * PER + LS_COLS + 2) + LS_AHEAD * LS_COLS + LS_AHEAD);
     // 16-byte copies where every row and head of q, k and v starts on a 16-byte boundary, 4-byte copies otherwise
     const int vec_ok = dk % 4 == 0 && dv % 4 == 0 && ldq % 4 == 0 && ldk % 4 == 0 && ldv % 4 == 0 &&
                        (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15) == 0;
@@ -477,11 +485,22 @@ __global__ void linear_state_carry_kernel(float* __restrict__ scratch, const flo
     const int first = req_chunks[2 * r], count = req_chunks[2 * r + 1];
     float* st = state + (size_t)slots[r] * state_stride + i;
     float S = positions[chunk_meta[4 * first]] == 0 ? 0.0f : *st;
-    for (int c = first; c < first + count; ++c) {
-        float* p = scratch + (size_t)c * size + i;
-        const float add = *p;
-        *p = S;
-        S = fmaf(gain[(size_t)c * H + h], S, add);
+    // eight chunks' loads in flight at a time: they do not depend on the carried value
+    for (int c0 = first; c0 < first + count; c0 += 8) {
+        float add[8], gn[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const bool in = c0 + j < first + count;
+            add[j] = in ? scratch[(size_t)(c0 + j) * size + i] : 0.0f;
+            gn[j] = in ? gain[(size_t)(c0 + j) * H + h] : 1.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (c0 + j < first + count) {
+                scratch[(size_t)(c0 + j) * size + i] = S;
+                S = fmaf(gn[j], S, add[j]);
+            }
+        }
     }
     *st = S;
 }
