@@ -15,7 +15,7 @@
 #include "common.cuh"
 
 #define LS_MAX_TAPS 8
-#define LS_AHEAD 16      // tokens staged in shared memory per round
+#define LS_AHEAD 16      // tokens staged in shared memory at a time
 #define LS_COLS 16       // columns of S per block
 
 __device__ __forceinline__ float ls_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
@@ -238,9 +238,9 @@ MM_EXPORT int mm_angle_table(const void* positions, const void* freq, void* tabl
 // out [n, H*dv] fp32.  state: the slot's S as [H, dv, dk] at `state`, slots `state_stride` floats apart.
 //
 // A thread's entries of its column are i = 32 (e / 4) + 4 (lane % 8) + e % 4, e < PER: the eight lanes of a column
-// read q and k of a token as 16-byte words without bank conflicts.  The tokens of a request come in rounds of
-// LS_AHEAD through two shared-memory buffers filled by asynchronous copies, so a round's loads run under the round
-// before it; within a round nothing but the eight-lane sums synchronises, and the loop over tokens is unrolled so
+// read q and k of a token as 16-byte words without bank conflicts.  The tokens of a request come in batches of
+// LS_AHEAD through two shared-memory buffers filled by asynchronous copies, so a batch's loads run under the batch
+// before it; within a batch nothing but the eight-lane sums synchronises, and the loop over tokens is unrolled so
 // that the sums of neighbouring tokens overlap (without the delta rule only S itself is carried from token to token).
 __device__ __forceinline__ void ls_cp_async4(void* smem, const void* gmem) {
     const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem);
@@ -267,10 +267,10 @@ __global__ void __launch_bounds__(128) linear_state_walk_kernel(
     float* __restrict__ state, long long state_stride, const int32_t* __restrict__ req_meta, const int32_t* __restrict__ slots,
     const int32_t* __restrict__ positions, int H, int Gq, int dk, int dv, int vec_ok, float* __restrict__ chunk_gain) {
     constexpr int DKP = 8 * PER;
-    constexpr int ROUND = LS_AHEAD * (2 * DKP + LS_COLS + 2);      // floats of one buffer: q, k, v, decay, write strength
+    constexpr int STAGE = LS_AHEAD * (2 * DKP + LS_COLS + 2);      // floats of one buffer: q, k, v, decay, write strength
     extern __shared__ __align__(16) float ls_smem[];
-    float* so = ls_smem + 2 * ROUND;                               // [AHEAD][COLS]
-    float* skq = so + LS_AHEAD * LS_COLS;                          // [AHEAD] k . q of the round's tokens
+    float* so = ls_smem + 2 * STAGE;                               // [AHEAD][COLS]
+    float* skq = so + LS_AHEAD * LS_COLS;                          // [AHEAD] k . q of the batch's tokens
 
     const int h = blockIdx.y, r = blockIdx.z;
     const int col0 = blockIdx.x * LS_COLS;
@@ -294,11 +294,11 @@ __global__ void __launch_bounds__(128) linear_state_walk_kernel(
         S[e] = (col_ok && i < dk && !fresh) ? st[i] : 0.0f;
     }
     // what no copy writes (entries beyond dk, columns beyond dv) stays zero in both buffers
-    for (int i = threadIdx.x; i < 2 * ROUND; i += 128) ls_smem[i] = 0.0f;
+    for (int i = threadIdx.x; i < 2 * STAGE; i += 128) ls_smem[i] = 0.0f;
     __syncthreads();
 
     auto fill = [&](int buf, int base) {
-        float* sq = ls_smem + buf * ROUND;
+        float* sq = ls_smem + buf * STAGE;
         float* sk = sq + LS_AHEAD * DKP;
         float* sv = sk + LS_AHEAD * DKP;
         float* sg = sv + LS_AHEAD * LS_COLS;
@@ -350,13 +350,13 @@ __global__ void __launch_bounds__(128) linear_state_walk_kernel(
             ls_cp_wait<0>();
         }
         __syncthreads();
-        const float* sq = ls_smem + buf * ROUND;
+        const float* sq = ls_smem + buf * STAGE;
         const float* sk = sq + LS_AHEAD * DKP;
         const float* sv = sk + LS_AHEAD * DKP;
         const float* sg = sv + LS_AHEAD * LS_COLS;
         const float* sb = sg + LS_AHEAD;
         if (MODE != 1) {
-            // k . q of every token of the round, once for all columns: a warp takes every fourth token
+            // k . q of every token of the batch, once for all columns: a warp takes every fourth token
             for (int tt = warp; tt < cnt; tt += 4) {
                 float d = 0.0f;
                 for (int i = lane; i < DKP; i += 32) d = fmaf(sk[tt * DKP + i], sq[tt * DKP + i], d);

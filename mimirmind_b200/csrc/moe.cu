@@ -282,7 +282,7 @@ __global__ void moe_sort_kernel(const int32_t* __restrict__ idx, int n_rows, int
         }
         return;
     }
-    // many experts: the rows are taken in rounds of blockDim.x, and the warps of a round take their turn
+    // many experts: the rows are taken blockDim.x at a time, and the warps take their turn
     for (int base = 0; base < n_rows; base += blockDim.x) {
         const int r = base + threadIdx.x;
         const int e = r < n_rows ? idx[r] : -1;
