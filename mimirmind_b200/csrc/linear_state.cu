@@ -260,39 +260,48 @@ __device__ __forceinline__ void ls_cp_wait() { asm volatile("cp.async.wait_group
 // the chunk adds): MODE 1 walks chunk blockIdx.z from zero and leaves what it adds, and the product of its decays, in
 // scratch; a carry kernel then walks each request's chunks in order, leaves every chunk's starting state in scratch and
 // the last state in the slot; MODE 2 walks every chunk again from its starting state and writes the outputs.
-template <int PER, bool DELTA, int MODE>
+// CPT: columns per thread (a thread of the chunk passes owns two columns, 16 apart, and reads q and k once for both: those
+// passes are bound by the shared-memory reads)
+template <int PER, bool DELTA, int MODE, int CPT>
 __global__ void __launch_bounds__(128) linear_state_walk_kernel(
     const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, int ldq, int ldk, int ldv,
     const float* __restrict__ gate, const float* __restrict__ beta, const float* __restrict__ head_decay, float* __restrict__ out,
     float* __restrict__ state, long long state_stride, const int32_t* __restrict__ req_meta, const int32_t* __restrict__ slots,
     const int32_t* __restrict__ positions, int H, int Gq, int dk, int dv, int vec_ok, float* __restrict__ chunk_gain) {
     constexpr int DKP = 8 * PER;
-    constexpr int STAGE = LS_AHEAD * (2 * DKP + LS_COLS + 2);      // floats of one buffer: q, k, v, decay, write strength
+    constexpr int COLS = LS_COLS * CPT;
+    constexpr int STAGE = LS_AHEAD * (2 * DKP + COLS + 2);      // floats of one buffer: q, k, v, decay, write strength
     extern __shared__ __align__(16) float ls_smem[];
     float* so = ls_smem + 2 * STAGE;                               // [AHEAD][COLS]
-    float* skq = so + LS_AHEAD * LS_COLS;                          // [AHEAD] k . q of the batch's tokens
+    float* skq = so + LS_AHEAD * COLS;                          // [AHEAD] k . q of the batch's tokens
 
     const int h = blockIdx.y, r = blockIdx.z;
-    const int col0 = blockIdx.x * LS_COLS;
+    const int col0 = blockIdx.x * COLS;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ks = lane & 7, cl = warp * 4 + (lane >> 3);
-    const int col = col0 + cl;
-    const bool col_ok = col < dv;
+    bool col_ok[CPT];
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) col_ok[c] = col0 + cl + 16 * c < dv;
     const int gq = h / (H / Gq);
     // MODE 1, 2: r is a chunk, req_meta the chunk list (first token, tokens, ., .), state the scratch with one matrix set per chunk
     const int t0 = req_meta ? req_meta[4 * r] : r;
     const int n = req_meta ? req_meta[4 * r + 1] : 1;
-    float* st = state + (size_t)(MODE == 0 ? slots[r] : r) * state_stride + ((size_t)h * dv + (col_ok ? col : 0)) * dk;
+    float* st[CPT];
+#pragma unroll
+    for (int c = 0; c < CPT; ++c)
+        st[c] = state + (size_t)(MODE == 0 ? slots[r] : r) * state_stride + ((size_t)h * dv + (col_ok[c] ? col0 + cl + 16 * c : 0)) * dk;
     const bool fresh = MODE == 1 || (MODE == 0 && positions[t0] == 0);
     const float hd = head_decay ? head_decay[h] : 1.0f;
     float gain = 1.0f;
 
-    float S[PER];
+    float S[CPT][PER];
 #pragma unroll
-    for (int e = 0; e < PER; ++e) {
-        const int i = (e >> 2) * 32 + ks * 4 + (e & 3);
-        S[e] = (col_ok && i < dk && !fresh) ? st[i] : 0.0f;
-    }
+    for (int c = 0; c < CPT; ++c)
+#pragma unroll
+        for (int e = 0; e < PER; ++e) {
+            const int i = (e >> 2) * 32 + ks * 4 + (e & 3);
+            S[c][e] = (col_ok[c] && i < dk && !fresh) ? st[c][i] : 0.0f;
+        }
     // what no copy writes (entries beyond dk, columns beyond dv) stays zero in both buffers
     for (int i = threadIdx.x; i < 2 * STAGE; i += 128) ls_smem[i] = 0.0f;
     __syncthreads();
@@ -301,7 +310,7 @@ __global__ void __launch_bounds__(128) linear_state_walk_kernel(
         float* sq = ls_smem + buf * STAGE;
         float* sk = sq + LS_AHEAD * DKP;
         float* sv = sk + LS_AHEAD * DKP;
-        float* sg = sv + LS_AHEAD * LS_COLS;
+        float* sg = sv + LS_AHEAD * COLS;
         float* sb = sg + LS_AHEAD;
         const int cnt = min(LS_AHEAD, n - base);
         if (vec_ok) {
@@ -312,10 +321,10 @@ __global__ void __launch_bounds__(128) linear_state_walk_kernel(
                 ls_cp_async16(sq + tt * DKP + i, q + t * ldq + gq * dk + i);
                 ls_cp_async16(sk + tt * DKP + i, k + t * ldk + gq * dk + i);
             }
-            const int vcols = min(LS_COLS, dv - col0) >> 2;
+            const int vcols = min(COLS, dv - col0) >> 2;
             for (int idx = threadIdx.x; idx < cnt * vcols; idx += 128) {
                 const int tt = idx / vcols, c = (idx - tt * vcols) * 4;
-                ls_cp_async16(sv + tt * LS_COLS + c, v + (size_t)(t0 + base + tt) * ldv + h * dv + col0 + c);
+                ls_cp_async16(sv + tt * COLS + c, v + (size_t)(t0 + base + tt) * ldv + h * dv + col0 + c);
             }
         } else {
             for (int idx = threadIdx.x; idx < cnt * dk; idx += 128) {
@@ -324,10 +333,10 @@ __global__ void __launch_bounds__(128) linear_state_walk_kernel(
                 ls_cp_async4(sq + tt * DKP + i, q + t * ldq + gq * dk + i);
                 ls_cp_async4(sk + tt * DKP + i, k + t * ldk + gq * dk + i);
             }
-            const int vcols = min(LS_COLS, dv - col0);
+            const int vcols = min(COLS, dv - col0);
             for (int idx = threadIdx.x; idx < cnt * vcols; idx += 128) {
                 const int tt = idx / vcols, c = idx - tt * vcols;
-                ls_cp_async4(sv + tt * LS_COLS + c, v + (size_t)(t0 + base + tt) * ldv + h * dv + col0 + c);
+                ls_cp_async4(sv + tt * COLS + c, v + (size_t)(t0 + base + tt) * ldv + h * dv + col0 + c);
             }
         }
         if (threadIdx.x < cnt) {
@@ -353,7 +362,7 @@ __global__ void __launch_bounds__(128) linear_state_walk_kernel(
         const float* sq = ls_smem + buf * STAGE;
         const float* sk = sq + LS_AHEAD * DKP;
         const float* sv = sk + LS_AHEAD * DKP;
-        const float* sg = sv + LS_AHEAD * LS_COLS;
+        const float* sg = sv + LS_AHEAD * COLS;
         const float* sb = sg + LS_AHEAD;
         if (MODE != 1) {
             // k . q of every token of the batch, once for all columns: a warp takes every fourth token
@@ -370,59 +379,73 @@ __global__ void __launch_bounds__(128) linear_state_walk_kernel(
             const float4* q4 = reinterpret_cast<const float4*>(sq + tt * DKP) + ks;
             const float4* k4 = reinterpret_cast<const float4*>(sk + tt * DKP) + ks;
             float kk[PER];
-            float dq[4] = {0.0f, 0.0f, 0.0f, 0.0f}, dkk[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            float dq[CPT][4], dkk[CPT][4];
+#pragma unroll
+            for (int c = 0; c < CPT; ++c)
+#pragma unroll
+                for (int x = 0; x < 4; ++x) dq[c][x] = dkk[c][x] = 0.0f;
 #pragma unroll
             for (int j = 0; j < PER / 4; ++j) {
                 const float4 qv = q4[j * 8], kv = k4[j * 8];
                 kk[4 * j] = kv.x; kk[4 * j + 1] = kv.y; kk[4 * j + 2] = kv.z; kk[4 * j + 3] = kv.w;
-                dq[0] = fmaf(S[4 * j], qv.x, dq[0]); dq[1] = fmaf(S[4 * j + 1], qv.y, dq[1]);
-                dq[2] = fmaf(S[4 * j + 2], qv.z, dq[2]); dq[3] = fmaf(S[4 * j + 3], qv.w, dq[3]);
-                if (DELTA) {
-                    dkk[0] = fmaf(S[4 * j], kv.x, dkk[0]); dkk[1] = fmaf(S[4 * j + 1], kv.y, dkk[1]);
-                    dkk[2] = fmaf(S[4 * j + 2], kv.z, dkk[2]); dkk[3] = fmaf(S[4 * j + 3], kv.w, dkk[3]);
-                }
-            }
-            float sdq = (dq[0] + dq[1]) + (dq[2] + dq[3]);
-            float sdk = DELTA ? (dkk[0] + dkk[1]) + (dkk[2] + dkk[3]) : 0.0f;
-            if (MODE != 1) {
 #pragma unroll
-                for (int o = 1; o < 8; o <<= 1) {
-                    if (DELTA) sdk += __shfl_xor_sync(0xffffffffu, sdk, o);
-                    sdq += __shfl_xor_sync(0xffffffffu, sdq, o);
+                for (int c = 0; c < CPT; ++c) {
+                    dq[c][0] = fmaf(S[c][4 * j], qv.x, dq[c][0]); dq[c][1] = fmaf(S[c][4 * j + 1], qv.y, dq[c][1]);
+                    dq[c][2] = fmaf(S[c][4 * j + 2], qv.z, dq[c][2]); dq[c][3] = fmaf(S[c][4 * j + 3], qv.w, dq[c][3]);
+                    if (DELTA) {
+                        dkk[c][0] = fmaf(S[c][4 * j], kv.x, dkk[c][0]); dkk[c][1] = fmaf(S[c][4 * j + 1], kv.y, dkk[c][1]);
+                        dkk[c][2] = fmaf(S[c][4 * j + 2], kv.z, dkk[c][2]); dkk[c][3] = fmaf(S[c][4 * j + 3], kv.w, dkk[c][3]);
+                    }
                 }
             }
             const float g = sg[tt];
-            const float vv = sv[tt * LS_COLS + cl];
-            const float u = DELTA ? sb[tt] * (vv - g * sdk) : vv;
 #pragma unroll
-            for (int e = 0; e < PER; ++e) S[e] = fmaf(kk[e], u, g * S[e]);
+            for (int c = 0; c < CPT; ++c) {
+                float sdq = (dq[c][0] + dq[c][1]) + (dq[c][2] + dq[c][3]);
+                float sdk = DELTA ? (dkk[c][0] + dkk[c][1]) + (dkk[c][2] + dkk[c][3]) : 0.0f;
+                if (MODE != 1) {
+#pragma unroll
+                    for (int o = 1; o < 8; o <<= 1) {
+                        if (DELTA) sdk += __shfl_xor_sync(0xffffffffu, sdk, o);
+                        sdq += __shfl_xor_sync(0xffffffffu, sdq, o);
+                    }
+                }
+                const float vv = sv[tt * COLS + cl + 16 * c];
+                const float u = DELTA ? sb[tt] * (vv - g * sdk) : vv;
+#pragma unroll
+                for (int e = 0; e < PER; ++e) S[c][e] = fmaf(kk[e], u, g * S[c][e]);
+                if (MODE != 1 && ks == 0) so[tt * COLS + cl + 16 * c] = fmaf(u, skq[tt], g * sdq);     // S_new^T q = g S_old^T q + u (k . q)
+            }
             if (MODE == 1) gain *= g;
-            if (MODE != 1 && ks == 0) so[tt * LS_COLS + cl] = fmaf(u, skq[tt], g * sdq);     // S_new^T q = g S_old^T q + u (k . q)
         }
         __syncthreads();
         if (MODE != 1)
-            for (int idx = threadIdx.x; idx < cnt * LS_COLS; idx += 128) {
-                const int tt = idx / LS_COLS, c = idx - tt * LS_COLS;
+            for (int idx = threadIdx.x; idx < cnt * COLS; idx += 128) {
+                const int tt = idx / COLS, c = idx - tt * COLS;
                 if (col0 + c < dv) out[(size_t)(t0 + base + tt) * H * dv + h * dv + col0 + c] = so[idx];
             }
     }
     if (MODE == 1 && blockIdx.x == 0 && threadIdx.x == 0) chunk_gain[(size_t)r * H + h] = gain;
     if (MODE == 2) return;
-    if (col_ok) {
 #pragma unroll
-        for (int e = 0; e < PER; ++e) {
-            const int i = (e >> 2) * 32 + ks * 4 + (e & 3);
-            if (i < dk) st[i] = S[e];
+    for (int c = 0; c < CPT; ++c)
+        if (col_ok[c]) {
+#pragma unroll
+            for (int e = 0; e < PER; ++e) {
+                const int i = (e >> 2) * 32 + ks * 4 + (e & 3);
+                if (i < dk) st[c][i] = S[c][e];
+            }
         }
-    }
 }
 
-template <int PER, bool DELTA, int MODE>
-static void ls_walk_launch_one(dim3 grid, cudaStream_t s, size_t smem, const float* q, const float* k, const float* v, int ldq, int ldk, int ldv,
+template <int PER, bool DELTA, int MODE, int CPT>
+static void ls_walk_launch_one(dim3 grid, cudaStream_t s, const float* q, const float* k, const float* v, int ldq, int ldk, int ldv,
                                const float* gate, const float* beta, const float* head_decay, float* out, float* state, long long state_stride,
                                const int32_t* req_meta, const int32_t* slots, const int32_t* positions, int H, int Gq, int dk, int dv, int vec_ok,
                                float* chunk_gain) {
-    auto kernel = linear_state_walk_kernel<PER, DELTA, MODE>;
+    auto kernel = linear_state_walk_kernel<PER, DELTA, MODE, CPT>;
+    const size_t smem = sizeof(float) * (2 * LS_AHEAD * (2 * 8 * PER + LS_COLS * CPT + 2) + LS_AHEAD * LS_COLS * CPT + LS_AHEAD);
+    grid.x = (dv + LS_COLS * CPT - 1) / (LS_COLS * CPT);
     if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     mm_launch(kernel, grid, dim3(128), smem, s, q, k, v, ldq, ldk, ldv, gate, beta, head_decay, out, state, state_stride, req_meta, slots,
               positions, H, Gq, dk, dv, vec_ok, chunk_gain);
@@ -434,16 +457,15 @@ static void ls_walk_launch(bool delta, int mode, dim3 grid, cudaStream_t s, cons
                            const float* gate, const float* beta, const float* head_decay, float* out, float* state, long long state_stride,
                            const int32_t* req_meta, const int32_t* slots, const int32_t* positions, int H, int Gq, int dk, int dv,
                            float* chunk_gain) {
-    const size_t smem = sizeof(float) * (2 * LS_AHEAD * (2 * 8 * PER + LS_COLS + 2) + LS_AHEAD * LS_COLS + LS_AHEAD);
     // 16-byte copies where every row and head of q, k and v starts on a 16-byte boundary, 4-byte copies otherwise
     const int vec_ok = dk % 4 == 0 && dv % 4 == 0 && ldq % 4 == 0 && ldk % 4 == 0 && ldv % 4 == 0 &&
                        (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15) == 0;
-#define LS_ONE(D, M) ls_walk_launch_one<PER, D, M>(grid, s, smem, q, k, v, ldq, ldk, ldv, gate, beta, head_decay, out, state, state_stride, req_meta, \
+#define LS_ONE(D, M, C) ls_walk_launch_one<PER, D, M, C>(grid, s, q, k, v, ldq, ldk, ldv, gate, beta, head_decay, out, state, state_stride, req_meta, \
                                                    slots, positions, H, Gq, dk, dv, vec_ok, chunk_gain)
-    if (mode == 1) LS_ONE(false, 1);
-    else if (mode == 2) LS_ONE(false, 2);
-    else if (delta) LS_ONE(true, 0);
-    else LS_ONE(false, 0);
+    if (mode == 1) LS_ONE(false, 1, 2);
+    else if (mode == 2) LS_ONE(false, 2, 2);
+    else if (delta) LS_ONE(true, 0, 1);
+    else LS_ONE(false, 0, 1);
 #undef LS_ONE
 }
 
