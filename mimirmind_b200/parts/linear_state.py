@@ -21,7 +21,9 @@ One class covers the family; what differs between its members is a parameter:
   ``heads * value_dim`` (``all``) numbers, or None; ``gate_activation``: ``silu`` or ``sigmoid`` on ``W_g h``.
 
 All input projections are one product with an fp32 result; everything between it and the output projection is fp32
-(``csrc/linear_state.cu``, ``csrc/norm_gated.cu``).  q and k have ``qk_heads`` heads; head h reads q/k head ``h // (heads / qk_heads)``.
+(``csrc/linear_state.cu``, ``csrc/norm_gated.cu``).  A request's tokens are walked in order from its slot's state; long
+portions without the delta rule (whose update is a scaling and an addition) are cut into chunks that are walked side by
+side, except in float32 runs, which keep one order of operations whatever the cutting.  q and k have ``qk_heads`` heads; head h reads q/k head ``h // (heads / qk_heads)``.
 """
 from __future__ import annotations
 
